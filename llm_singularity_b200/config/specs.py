@@ -132,7 +132,12 @@ class KVAttentionSpec(PartSpec):
     0: none); a rotation (``position``).  A query sees the keys not after it that lie within
     ``window`` positions (None: all) and in its own chunk of ``chunk`` positions counted from the
     start of the sequence (None: no chunks).  ``out_gate``: the heads' outputs are multiplied by
-    sigmoid(W_g x) before the output projection."""
+    sigmoid(W_g x) before the output projection; with ``gate_per_head`` W_g has one row per head and
+    the gate is one number per head.  ``qk_norm_span`` "all": the norm of q (and of k) is one RMS
+    norm over all heads at once, before they are split, with a weight as long as the projection.
+    ``v_unit_norm``: each value head is divided by its root mean square (``eps``, no weight) and
+    cached so.  ``sink``: one is added to the softmax's denominator, a place with score 0 and no
+    value, so that a row's weights may sum to less than one."""
 
     hidden_size: int = 0
     num_heads: int = 0
@@ -149,6 +154,10 @@ class KVAttentionSpec(PartSpec):
     temp_every: int = 0
     out_gate: bool = False
     position: PartSpec = field(default_factory=NoPositionSpec)
+    qk_norm_span: str = "head"
+    v_unit_norm: bool = False
+    sink: bool = False
+    gate_per_head: bool = False
     kind: str = field(init=False, default="kv_attention")
 
 
@@ -176,15 +185,66 @@ class MatrixMemorySpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec(PartSpec):
+    """A delta-rule memory with one fade and one write strength per head and token (the gated delta
+    rule).  q and k have ``num_key_heads`` heads of ``key_dim`` (value head h reads key head
+    ``h // (num_heads / num_key_heads)``), v has ``num_heads`` heads of ``value_dim``.  Each of q, k, v
+    passes a causal convolution over time per channel (``conv_taps`` taps, zeros before the start)
+    and silu; q and k become unit vectors per head (``x / sqrt(sum x^2 + unit_eps)``), q also times
+    ``key_dim^-1/2``.  ``beta = sigmoid(W_b x)``, ``g = exp(-exp(A_log) * softplus(W_a x + dt_bias))``;
+
+        S <- g S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q
+
+    Each head's o is divided by its root mean square (``eps``), times one weight of ``value_dim``
+    shared by the heads, times silu(W_g x), then projected by W_o."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_key_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 1
+    eps: float = 1e-5
+    unit_eps: float = 1e-6
+    kind: str = field(init=False, default="gated_delta")
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec(PartSpec):
+    """A delta-rule memory with a decay and a removal rate per key channel (the generalized delta
+    rule).  r, k and v have ``num_heads`` heads of ``key_dim``.  With the unit key
+    ``u = k / sqrt(sum k^2 + unit_eps)``, the decay ``w = exp(-decay_rate * sigmoid(W_w2 tanh(W_w1 x)
+    + w0))`` (a projection through ``decay_rank`` hidden values) and ``a = sigmoid(W_a x + a_bias)``:
+
+        S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the state the token found)
+        o = S^T r
+
+    Each head's o is divided by its root mean square (``eps``), the heads are concatenated, times
+    one weight over all of them, times sigmoid(W_g x), then projected by W_o."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    key_dim: int = 0
+    decay_rank: int = 0
+    decay_rate: float = 0.6065306597126334          # e^(-1/2)
+    eps: float = 1e-5
+    unit_eps: float = 1e-6
+    kind: str = field(init=False, default="channel_delta")
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec(PartSpec):
-    """Mixers side by side on one input: each branch's result is RMS-normed over the model width
-    with a weight of its own (``eps``), and the mean of those is the mixer's result.  ``names`` are
-    the branches' names in parameter paths."""
+    """Mixers side by side on one input.  ``combine`` "normed_mean": each branch's result is
+    RMS-normed over the model width with a weight of its own (``eps``), and the mean of those is
+    the mixer's result; "weighted_sum": the results are added with the fixed factors ``scales``, no
+    norm and no parameters.  ``names`` are the branches' names in parameter paths."""
 
     hidden_size: int = 0
     branches: Tuple[PartSpec, ...] = ()
     names: Tuple[str, ...] = ()
     eps: float = 1e-5
+    combine: str = "normed_mean"
+    scales: Tuple[float, ...] = ()
     kind: str = field(init=False, default="parallel")
 
 
@@ -218,6 +278,19 @@ class GatedMLPSpec(PartSpec):
     intermediate_size: int = 0
     activation: str = "silu"
     kind: str = field(init=False, default="gated_mlp")
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec(PartSpec):
+    """down( act(up(x)) ), dense, no gate and no bias.  ``activation`` "bent_square" is a two-branch
+    activation with two learnt numbers p and q stored with the layer: ``softplus(p) z^2 + z/2`` for
+    z > 0 and ``(1/2 + softplus(q)) (e^z - 1 - z) + z/2`` for z <= 0; "silu", "gelu_tanh" and "none"
+    need no parameter."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "bent_square"
+    kind: str = field(init=False, default="dense_mlp")
 
 
 @dataclass(frozen=True)
@@ -258,12 +331,13 @@ class TokenSideSpec(PartSpec):
 # --------------------------------------------------------------------------- blocks
 @dataclass(frozen=True)
 class BlockSpec(PartSpec):
-    """x += mixer(norm1(x)); x += ffn(norm2(x))   (the "pre_norm" arrangement)."""
+    """x += mixer(norm1(x)); x += ffn(norm2(x))   (the "pre_norm" arrangement).  ``ffn`` None: the
+    block has its first sublayer only."""
 
     mixer: PartSpec = None
-    ffn: PartSpec = None
+    ffn: Optional[PartSpec] = None
     mixer_norm: PartSpec = None
-    ffn_norm: PartSpec = None
+    ffn_norm: Optional[PartSpec] = None
     kind: str = field(init=False, default="pre_norm")
 
 
@@ -337,6 +411,7 @@ class HeadSpec(PartSpec):
     hidden_size: int = 0
     tied: bool = False            # reuse the embedding table as the projection
     norm: PartSpec = None
+    logit_softcap: Optional[float] = None     # logits <- cap * tanh(logits / cap)
     kind: str = field(init=False, default="lm_head")
 
 

@@ -49,3 +49,55 @@ LSB_API int lsb_gated_act(const void* gate_up, void* out, int dtype, int tokens,
                                                 (const T*)gate_up, (T*)out, inter, total, act));
     return 0;
 }
+
+// A plain (ungated) activation on every element, evaluated in 32-bit.  LSB_ACT_BENT_SQUARE is a
+// two-branch activation with two learnt numbers handed in already transformed: right of zero a
+// parabola, c_pos z^2 + z / 2; left of it a saturating branch, c_neg (e^z - 1 - z) + z / 2
+// (c_pos = softplus(p), c_neg = 1/2 + softplus(q) for the stored p and q).
+enum : int { LSB_ACT_BENT_SQUARE = 4 };
+
+template <typename T>
+__global__ void plain_act_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int act, float c_pos, float c_neg) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const float z = lsb_to_float(x[idx]);
+        float a;
+        if (act == LSB_ACT_SILU) a = z / (1.f + expf(-z));
+        else if (act == LSB_ACT_GELU_TANH) a = 0.5f * z * (1.f + tanhf(0.7978845608f * (z + 0.044715f * z * z * z)));
+        else if (act == LSB_ACT_BENT_SQUARE) a = z > 0.f ? c_pos * z * z + 0.5f * z : c_neg * (expm1f(z) - z) + 0.5f * z;
+        else a = z;
+        out[idx] = lsb_from_float<T>(a);
+    }
+}
+
+LSB_API int lsb_plain_act(const void* x, void* out, int dtype, long long total, int act, float c_pos, float c_neg,
+                          cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (act < LSB_ACT_SILU || act > LSB_ACT_BENT_SQUARE) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    long long blocks = (total + threads - 1) / threads;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(plain_act_kernel<T>, dim3((int)blocks), dim3(threads), 0, stream, 1,
+                                                (const T*)x, (T*)out, total, act, c_pos, c_neg));
+    return 0;
+}
+
+// x <- cap * tanh(x / cap) in place on 32-bit values (a soft cap on logits).
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const float inv = 1.f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+LSB_API int lsb_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    return lsb_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, 1, x, total, cap);
+}

@@ -8,7 +8,10 @@
 // reads kv head h / (nh / nkv); scores (q . k) * scale; softmax by running maximum and sum; the
 // weighted sum of values is divided by the sum at the end and, if a gate is given, multiplied by
 // sigmoid(gate[t, h * dv + c]) on the way out.  Keys are [page][kv head][offset][dk], values
-// [page][kv head][offset][dv].  Scores, weights and sums are 32-bit.
+// [page][kv head][offset][dv].  Scores, weights and sums are 32-bit.  Two options ride in `flags`:
+// kDvSink adds one to the softmax's denominator (a place with score 0 and no value, so a row's weights
+// sum to less than one), kDvGateHeads reads one gate number per head, gate[t, h], instead of one per
+// output channel.
 //
 // Generic form (any sizes, 32-bit or bfloat16 storage): one warp owns a (row, head); lanes split
 // the keys of a 32-key stretch for the scores and the value dims for the weighted sum.
@@ -33,6 +36,7 @@ LSB_DEFINE_STATUS()
 
 constexpr int kDvWarps = 4;
 constexpr int kDvMaxDim = 256;
+constexpr int kDvSink = 1, kDvGateHeads = 2;
 
 template <typename T>
 __device__ __forceinline__ float dv_dot(const float* __restrict__ q, const T* __restrict__ k, int n, bool vec) {
@@ -67,7 +71,7 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
                             const int* __restrict__ table_rows, const int* __restrict__ block_table, int table_stride,
                             const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
                             int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
-                            int chunk, int vec) {
+                            int chunk, int vec, int flags) {
     __shared__ float q_sh[kDvWarps][kDvMaxDim];
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
@@ -128,15 +132,17 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
         }
         m = m_new;
     }
+    if (flags & kDvSink) l += expf(-m);                      // the sink's weight relative to the maximum (inf: all weights vanish)
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* o = out + ((size_t)t * nh + h) * dv;
-    const T* gr = gate ? gate + (size_t)t * gate_stride + (size_t)h * dv : nullptr;
+    const bool per_head = (flags & kDvGateHeads) != 0;
+    const T* gr = gate ? gate + (size_t)t * gate_stride + (per_head ? (size_t)h : (size_t)h * dv) : nullptr;
 #pragma unroll
     for (int c = 0; c < kAccs; ++c) {
         const int d = lane + 32 * c;
         if (d < dv) {
             float y = acc[c] * inv;
-            if (gr) y *= 1.f / (1.f + expf(-lsb_to_float(gr[d])));
+            if (gr) y *= 1.f / (1.f + expf(-lsb_to_float(gr[per_head ? 0 : d])));
             o[d] = lsb_from_float<T>(y);
         }
     }
@@ -168,7 +174,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int table_stride,
                         const __nv_bfloat16* __restrict__ gate, long long gate_stride,
                         __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
-                        int num_pages, float scale_log2, int window, int chunk, int ksplit, float* __restrict__ scratch) {
+                        int num_pages, float scale_log2, int window, int chunk, int ksplit, float* __restrict__ scratch,
+                        int flags) {
     constexpr int KS = DKP + 8, VS = DVP + 8;          // row strides in elements: 4 words past a multiple of 32
     extern __shared__ __align__(16) unsigned char dv_smem[];
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(dv_smem);       // [STAGES][64][KS]
@@ -176,6 +183,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int r = blockIdx.z, g = blockIdx.y, group = nh / nkv;
+    const bool sink = (flags & kDvSink) != 0, per_head = (flags & kDvGateHeads) != 0;
+    const int gate_w = per_head ? 1 : dv;              // gate numbers a head has
     const int qs = q_start[r];
     const int q_len = q_start[r + 1] - qs;
     const int rows_total = q_len * group;
@@ -197,7 +206,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     };
     const int last_row = min(tile_row0 + block_rows, rows_total) - 1;
     const int last_pos = p_base + last_row / group;
-    int kt0 = lowest(p_base + tile_row0 / group) / kMmaKeys, kt1 = last_pos / kMmaKeys;
+    const int key_lo = lowest(p_base + tile_row0 / group);            // the first key any row of the block sees
+    int kt0 = key_lo / kMmaKeys, kt1 = last_pos / kMmaKeys;
     if (NARROW && ksplit > 1) {                       // this block's share of the key tiles (it may be empty)
         const int per = (kt1 - kt0 + ksplit) / ksplit;
         kt0 += key_part * per;
@@ -249,7 +259,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     constexpr int kNoRow = -2, kPastEnd = -1;          // a page id a request never holds / nothing to load
     auto place = [&](int kt) -> int {
         const int kj = kt * kMmaKeys + my_row;
-        if (kt > kt1 || kj > last_pos) return kPastEnd;
+        // (keys behind every row's window are never looked up: their pages may have gone back to the pool)
+        if (kt > kt1 || kj > last_pos || kj < key_lo) return kPastEnd;
         const int page = bt[kj / page_size];
         return page < 0 ? kNoRow : page;
     };
@@ -434,23 +445,33 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 }
                 continue;
             }
+            if (sink) den += exp2f(-mm);
             float y = den > 0.f ? num / den : 0.f;
             const size_t t = (size_t)qs + row / group;
             const int h = g * group + row % group;
-            if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (size_t)h * dv + c])));
+            if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (size_t)h * gate_w + (per_head ? 0 : c)])));
             out[(t * nh + h) * dv + c] = __float2bfloat16_rn(y);
         }
         return;
     }
     if (!active) return;
+    if (sink) {
+        l_a += exp2f(-m_a);
+        l_b += exp2f(-m_b);
+    }
     const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+    float gh_a = 1.f, gh_b = 1.f;                      // one gate number per head
+    if (gate && per_head) {
+        if (ok_a) gh_a = 1.f / (1.f + __expf(-__bfloat162float(gate[t_a * gate_stride + h_a])));
+        if (ok_b) gh_b = 1.f / (1.f + __expf(-__bfloat162float(gate[t_b * gate_stride + h_b])));
+    }
 #pragma unroll
     for (int nb = 0; nb < DVP / 8; ++nb) {
         if (nb < dv_blocks) {
             const int c = nb * 8 + 2 * tid4;
             if (ok_a) {
-                float y0 = o[nb][0] * inv_a, y1 = o[nb][1] * inv_a;
-                if (gate) {
+                float y0 = o[nb][0] * inv_a * gh_a, y1 = o[nb][1] * inv_a * gh_a;
+                if (gate && !per_head) {
                     const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t_a * gate_stride + (size_t)h_a * dv + c));
                     y0 *= 1.f / (1.f + __expf(-gv.x));
                     y1 *= 1.f / (1.f + __expf(-gv.y));
@@ -458,8 +479,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 *reinterpret_cast<__nv_bfloat162*>(out + (t_a * nh + h_a) * dv + c) = __floats2bfloat162_rn(y0, y1);
             }
             if (ok_b) {
-                float y0 = o[nb][2] * inv_b, y1 = o[nb][3] * inv_b;
-                if (gate) {
+                float y0 = o[nb][2] * inv_b * gh_b, y1 = o[nb][3] * inv_b * gh_b;
+                if (gate && !per_head) {
                     const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t_b * gate_stride + (size_t)h_b * dv + c));
                     y0 *= 1.f / (1.f + __expf(-gv.x));
                     y1 *= 1.f / (1.f + __expf(-gv.y));
@@ -476,7 +497,7 @@ constexpr int kMaxParts = 8;
 __global__ void __launch_bounds__(kMmaThreads)
 attention_dv_merge_kernel(const float* __restrict__ scratch, const int* __restrict__ q_start,
                           const __nv_bfloat16* __restrict__ gate, long long gate_stride,
-                          __nv_bfloat16* __restrict__ out, int nh, int nkv, int dv, int ksplit) {
+                          __nv_bfloat16* __restrict__ out, int nh, int nkv, int dv, int ksplit, int flags) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int r = blockIdx.z, g = blockIdx.y, group = nh / nkv;
@@ -507,10 +528,12 @@ attention_dv_merge_kernel(const float* __restrict__ scratch, const int* __restri
             num += f * pv[p];
             den += f * pl[p];
         }
+        if (flags & kDvSink) den += exp2f(-mm);
         float y = den > 0.f ? num / den : 0.f;
         const size_t t = (size_t)qs + row / group;
         const int h = g * group + row % group;
-        if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (size_t)h * dv + c])));
+        const bool per_head = (flags & kDvGateHeads) != 0;
+        if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (per_head ? (size_t)h : (size_t)h * dv + c)])));
         out[(t * nh + h) * dv + c] = __float2bfloat16_rn(y);
     }
 }
@@ -549,7 +572,7 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
                                  const int* kv_len, const int* table_rows, const int* block_table, int table_stride,
                                  const void* gate, long long gate_stride, void* out, int n_requests, int max_q_len,
                                  int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
-                                 int chunk, int sms, int shape, float* scratch, cudaStream_t stream) {
+                                 int chunk, int sms, int shape, float* scratch, int flags, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (sms <= 0) sms = 148;
     if (!lsb_attention_dv_mma_supported(dk, dv) || nkv <= 0 || nh % nkv || window < 0 || chunk < 0 || n_requests > 65535 ||
@@ -576,7 +599,7 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
                           stream, 1, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,                     \
                           (const __nv_bfloat16*)v_pages, q_start, kv_len, table_rows, block_table, table_stride, \
                           (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, nh, nkv, dk, dv,         \
-                          page_size, num_pages, scale_log2, window, chunk, ksplit, scratch);                     \
+                          page_size, num_pages, scale_log2, window, chunk, ksplit, scratch, flags);              \
     } while (0)
 #define LSB_DV_MMA_SHAPE(DKP, DVP)                                                                               \
     do {                                                                                                         \
@@ -599,7 +622,7 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
     if (rc || ksplit <= 1) return rc;
     return lsb_launch(attention_dv_merge_kernel, dim3(tiles, nkv, n_requests), dim3(kMmaThreads), 0, stream, 1,
                       (const float*)scratch, q_start, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, nh, nkv,
-                      dv, ksplit);
+                      dv, ksplit, flags);
 }
 
 LSB_API int lsb_attention_dv_max_dim() { return kDvMaxDim; }
@@ -610,7 +633,7 @@ LSB_API int lsb_attention_dv_generic(const void* q, const void* k_pages, const v
                                      const int* kv_len, const int* table_rows, const int* block_table,
                                      int table_stride, const void* gate, long long gate_stride, void* out, int dtype,
                                      int n_requests, int max_q_len, int nh, int nkv, int dk, int dv, int page_size,
-                                     int num_pages, float scale, int window, int chunk, cudaStream_t stream) {
+                                     int num_pages, float scale, int window, int chunk, int flags, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (dk <= 0 || dk > kDvMaxDim || dv <= 0 || dv > kDvMaxDim || nkv <= 0 || nh % nkv || window < 0 || chunk < 0)
         return (int)cudaErrorInvalidValue;
@@ -621,6 +644,6 @@ LSB_API int lsb_attention_dv_generic(const void* q, const void* k_pages, const v
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
         attention_dv_generic_kernel<T>, grid, dim3(kDvWarps * 32), 0, stream, 1, (const T*)q, (const T*)k_pages,
         (const T*)v_pages, q_start, kv_len, table_rows, block_table, table_stride, (const T*)gate, gate_stride,
-        (T*)out, nh, nkv, dk, dv, page_size, num_pages, scale, window, chunk, vec));
+        (T*)out, nh, nkv, dk, dv, page_size, num_pages, scale, window, chunk, vec, flags));
     return 0;
 }

@@ -3,7 +3,9 @@
 //
 //   * a bias per channel (q, k, v), added in 32-bit;
 //   * a norm per head of q and of k: z / sqrt(mean(z^2) + eps) * w, one weight of head size for
-//     all heads of q and one for all heads of k;
+//     all heads of q and one for all heads of k; or (`norm_all`) one norm over all heads of q at
+//     once and one over all heads of k, with weights as long as the whole projection;
+//   * each value head divided by its root mean square (`v_unit`: no weight, the same eps);
 //   * a query temperature: q *= 1 + coef * ln(floor((pos + 1) / every) + 1);
 //   * rotation of the first `rotary_dim` dims of every q and k head by pos * inv_freq[i], pairs
 //     (2i, 2i + 1) ("adjacent") or (i, i + rotary_dim / 2) ("half"), angle formed in 32-bit;
@@ -26,6 +28,7 @@ struct PrepArgs {
     int nh, nkv, dk, dv;
     const float *q_bias, *k_bias, *v_bias;
     const float *q_norm, *k_norm; float norm_eps;
+    int norm_all, v_unit;
     float temp_coef; int temp_every;
     const float* inv_freq; int rotary_dim, adjacent;
     const int *positions, *token_req, *table_rows, *block_table; int table_stride;
@@ -58,6 +61,7 @@ template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArgs a) {
     extern __shared__ float all_sh[];                   // [(nh + nkv) * dk]
     __shared__ float cs_sh[2][kPrepMaxDim / 2];
+    __shared__ float sum_sh[33];
     lsb_pdl_launch_dependents();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // positions are metadata of the step (on the device before its first kernel starts): the
@@ -146,13 +150,27 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
         all_sh[i] = x;
     }
     __syncthreads();
+    float inv_all_q = 1.f, inv_all_k = 1.f;
+    if (a.norm_all && a.q_norm) {                       // one mean of squares over all of q, one over all of k
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < nall; i += kPrepWarps * 32) {
+            const float x = all_sh[i];
+            if (i < nq) sq += x * x;
+            else sk += x * x;
+        }
+        inv_all_q = rsqrtf(lsb_block_sum(sq, sum_sh) / (float)nq + a.norm_eps);
+        inv_all_k = rsqrtf(lsb_block_sum(sk, sum_sh) / (float)(nall - nq) + a.norm_eps);
+    }
     for (int head = warp; head < a.nh + a.nkv; head += kPrepWarps) {
         const bool is_q = head < a.nh;
         const int hh = is_q ? head : head - a.nh;
         const float* hs = all_sh + (size_t)head * a.dk;
         const float* nw = is_q ? a.q_norm : a.k_norm;
+        if (nw && a.norm_all) nw += (size_t)hh * a.dk;
         float inv = 1.f;
-        if (nw) {
+        if (nw && a.norm_all) {
+            inv = is_q ? inv_all_q : inv_all_k;
+        } else if (nw) {
             float ss = 0.f;
             for (int d = lane; d < a.dk; d += 32) ss += hs[d] * hs[d];
             inv = rsqrtf(lsb_warp_sum(ss) / (float)a.dk + a.norm_eps);
@@ -191,7 +209,23 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
             }
         }
     }
-    if (v_base >= 0 && a.vec && !a.v_bias) {
+    if (v_base >= 0 && a.v_unit) {
+        const T* v = row + a.v_off;
+        for (int head = warp; head < a.nkv; head += kPrepWarps) {
+            float ss = 0.f;
+            for (int d = lane; d < a.dv; d += 32) {
+                float x = lsb_to_float(v[head * a.dv + d]);
+                if (a.v_bias) x += a.v_bias[head * a.dv + d];
+                ss += x * x;
+            }
+            const float inv = rsqrtf(lsb_warp_sum(ss) / (float)a.dv + a.norm_eps);
+            for (int d = lane; d < a.dv; d += 32) {
+                float x = lsb_to_float(v[head * a.dv + d]);
+                if (a.v_bias) x += a.v_bias[head * a.dv + d];
+                ((T*)a.v_pages)[v_base + (long long)head * a.page_size * a.dv + d] = lsb_from_float<T>(x * inv);
+            }
+        }
+    } else if (v_base >= 0 && a.vec && !a.v_bias) {
         const T* v = row + a.v_off;
         for (int w = threadIdx.x * VEC; w < a.nkv * a.dv; w += blockDim.x * VEC) {
             const int head = w / a.dv, d = w - head * a.dv;
@@ -214,7 +248,7 @@ LSB_API int lsb_attention_prep_max_dim() { return kPrepMaxDim; }
 LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_off, int k_off, int v_off, int tokens,
                                int nh, int nkv, int dk, int dv, const float* q_bias, const float* k_bias,
                                const float* v_bias, const float* q_norm, const float* k_norm, float norm_eps,
-                               float temp_coef, int temp_every, const float* inv_freq, int rotary_dim, int adjacent,
+                               int norm_all, int v_unit, float temp_coef, int temp_every, const float* inv_freq, int rotary_dim, int adjacent,
                                const int* positions, const int* token_req, const int* table_rows,
                                const int* block_table, int table_stride, void* q_out, void* k_pages, void* v_pages,
                                int page_size, int num_pages, int store, cudaStream_t stream) {
@@ -227,6 +261,7 @@ LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_
     a.nh = nh; a.nkv = nkv; a.dk = dk; a.dv = dv;
     a.q_bias = q_bias; a.k_bias = k_bias; a.v_bias = v_bias;
     a.q_norm = q_norm; a.k_norm = k_norm; a.norm_eps = norm_eps;
+    a.norm_all = norm_all; a.v_unit = v_unit;
     a.temp_coef = temp_coef; a.temp_every = temp_every;
     a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.adjacent = adjacent;
     a.positions = positions; a.token_req = token_req; a.table_rows = table_rows; a.block_table = block_table;

@@ -1,0 +1,426 @@
+// Delta-rule memories: a matrix state S [key channels, value channels] per head and request that a
+// token first lets fade, then corrects along a key, then reads.  Two forms share the walk:
+//
+//   scalar gates (MODE 0):   S <- g S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q
+//       g and beta one number per token and head; q and k unit vectors of a key head that several
+//       value heads may share (value head h reads key head h / (heads / key_heads))
+//   channel gates (MODE 1):  S <- diag(w) S - (a * u) (u^T S) + k v^T;  o = S^T r
+//       w and a one number per key channel, u the unit vector along k; both terms read the state the
+//       token found
+//
+// for any mix of prompt portions and single decode tokens, each request continuing from the state
+// its slot holds.  S is 32-bit, stored [slot, head, value channel, key channel] (key channels
+// contiguous).  Everything that enters the walk is formed in 32-bit by a preparation kernel from the
+// projections' outputs:
+//
+//   gated_delta_prep    a short causal convolution per channel over time (taps [channels, n], the
+//                       last one meets the current token; the n - 1 inputs before a portion come from
+//                       the slot's convolution state, zeros at a request's start), silu, unit length
+//                       per key head (q also times key_dim^-1/2), beta = sigmoid(.), and the fade
+//                       g = exp(-exp(A_log) * softplus(. + dt_bias))
+//   conv_state_update   the slot's last n - 1 inputs after the step
+//   channel_delta_prep  u = k / sqrt(sum k^2 + eps), a = sigmoid(. + bias), w = exp(-rate * sigmoid(. + w0))
+//   delta_output        each head's read-out divided by its root mean square, times a weight, times
+//                       sigmoid or silu of a gate projection
+//   tanh_rows           the hidden activation of a two-step (low-rank) projection
+//
+// The walk: a block owns (request, head, a tile of value columns) and takes the request's tokens in
+// order, so the result does not depend on how a prompt was cut.  A column's key channels are dealt to
+// `split` neighbouring lanes, 32 each, kept in registers; dots are finished by shuffles.  The tokens'
+// vectors come through shared memory in chunks of 16 tokens.
+#include "common.cuh"
+
+LSB_DEFINE_STATUS()
+
+constexpr int kDeltaThreads = 128;
+constexpr int kDeltaChunk = 16;      // tokens staged at a time
+constexpr int kDeltaPer = 32;        // key channels of a column that one lane keeps
+constexpr int kDeltaPad = 4;         // words between the shares of neighbouring lanes in shared memory
+constexpr int kDeltaMaxSplit = 8;
+
+__device__ __forceinline__ float delta_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float delta_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// ------------------------------------------------------------------ scalar gates: preparation
+struct GatedPrepArgs {
+    const void* proj; long long ld; int q_off, k_off, v_off;
+    int G, H, D, V, taps;
+    const float *q_taps, *k_taps, *v_taps;         // [channels, taps]
+    float* conv_state; int n_slots;                 // [slots, taps - 1, 2 G D + H V]
+    const float* raw; long long raw_ld;             // [T, 2 H]: beta's projection, then the fade's
+    const float *a_log, *dt_bias;
+    const int *token_req, *q_start, *table_rows;
+    float *qk_out, *v_out, *scal_out;               // [T, 2 G D], [T, H V], [T, 2 H]
+    float unit_eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kDeltaThreads) gated_delta_prep_kernel(GatedPrepArgs a) {
+    extern __shared__ float ch_sh[];                // the token's channels after convolution and silu
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.token_req[t];
+    const int t0 = a.q_start[r], i = t - t0;
+    const int slot = a.table_rows[r];
+    if (slot < 0 || slot >= a.n_slots) {
+        if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    const int GD = a.G * a.D, C = 2 * GD + a.H * a.V, m = a.taps - 1;
+    const T* proj = (const T*)a.proj;
+    const float* old = a.conv_state + (size_t)slot * m * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        int lc, off;
+        const float* taps;
+        if (c < GD) { lc = c; off = a.q_off; taps = a.q_taps; }
+        else if (c < 2 * GD) { lc = c - GD; off = a.k_off; taps = a.k_taps; }
+        else { lc = c - 2 * GD; off = a.v_off; taps = a.v_taps; }
+        float acc = 0.f;
+        for (int j = 0; j < a.taps; ++j) {
+            const int ii = i - (m - j);             // the portion's token this tap meets
+            const float x = ii >= 0 ? lsb_to_float(proj[(size_t)(t0 + ii) * a.ld + off + lc]) : old[(size_t)(m + ii) * C + c];
+            acc += taps[(size_t)lc * a.taps + j] * x;
+        }
+        ch_sh[c] = acc * delta_sigmoid(acc);
+    }
+    __syncthreads();
+    for (int head = warp; head < 2 * a.G; head += kDeltaThreads / 32) {
+        const float* hs = ch_sh + (size_t)head * a.D;
+        float ss = 0.f;
+        for (int d = lane; d < a.D; d += 32) ss += hs[d] * hs[d];
+        float inv = rsqrtf(lsb_warp_sum(ss) + a.unit_eps);
+        if (head < a.G) inv *= rsqrtf((float)a.D);
+        for (int d = lane; d < a.D; d += 32) a.qk_out[(size_t)t * 2 * GD + (size_t)head * a.D + d] = hs[d] * inv;
+    }
+    for (int c = threadIdx.x; c < a.H * a.V; c += blockDim.x) a.v_out[(size_t)t * a.H * a.V + c] = ch_sh[2 * GD + c];
+    for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+        const float zb = a.raw[(size_t)t * a.raw_ld + h], za = a.raw[(size_t)t * a.raw_ld + a.H + h];
+        a.scal_out[(size_t)t * 2 * a.H + h] = expf(-expf(a.a_log[h]) * delta_softplus(za + a.dt_bias[h]));
+        a.scal_out[(size_t)t * 2 * a.H + a.H + h] = delta_sigmoid(zb);
+    }
+}
+
+// The last taps - 1 inputs of every request of the step, for the next step: from the portion where it
+// is long enough, from the old state (moved up) where it is not.
+template <typename T>
+__global__ void __launch_bounds__(kDeltaThreads)
+conv_state_update_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, int GD, int HV,
+                         int taps, float* __restrict__ conv_state, int n_slots, const int* __restrict__ q_start,
+                         const int* __restrict__ table_rows) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.y;
+    const int t0 = q_start[r], L = q_start[r + 1] - t0, m = taps - 1;
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= n_slots || L <= 0) return;
+    const int C = 2 * GD + HV;
+    float* st = conv_state + (size_t)slot * m * C;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < C; c += gridDim.x * blockDim.x) {
+        const int col = c < GD ? q_off + c : c < 2 * GD ? k_off + c - GD : v_off + c - 2 * GD;
+        // (ascending j: what entry j takes from the old state lies at j + L, not yet written)
+        for (int j = 0; j < m; ++j) {
+            const int ii = L - m + j;
+            st[(size_t)j * C + c] = ii >= 0 ? lsb_to_float(proj[(size_t)(t0 + ii) * ld + col]) : st[(size_t)(j + L) * C + c];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ channel gates: preparation
+struct ChannelPrepArgs {
+    const void* proj; long long ld; int r_off, k_off, v_off;
+    int H, D, V;
+    const float* decay_raw; long long decay_ld; const float* decay_bias;     // [T, H D] + [H D]
+    const float* remove_raw; long long remove_ld; const float* remove_bias;
+    float decay_rate, unit_eps;
+    float *vec_out, *v_out;                         // [T, H, 5, D]: r, k, u, a * u, w;  [T, H V]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kDeltaThreads) channel_delta_prep_kernel(ChannelPrepArgs a) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* row = (const T*)a.proj + (size_t)t * a.ld;
+    for (int h = warp; h < a.H; h += kDeltaThreads / 32) {
+        const T* k = row + a.k_off + (size_t)h * a.D;
+        float ss = 0.f;
+        for (int d = lane; d < a.D; d += 32) {
+            const float x = lsb_to_float(k[d]);
+            ss += x * x;
+        }
+        const float inv = rsqrtf(lsb_warp_sum(ss) + a.unit_eps);
+        float* o = a.vec_out + ((size_t)t * a.H + h) * 5 * a.D;
+        for (int d = lane; d < a.D; d += 32) {
+            const int c = h * a.D + d;
+            const float kd = lsb_to_float(k[d]), u = kd * inv;
+            const float rem = delta_sigmoid(a.remove_raw[(size_t)t * a.remove_ld + c] + a.remove_bias[c]);
+            const float w = expf(-a.decay_rate * delta_sigmoid(a.decay_raw[(size_t)t * a.decay_ld + c] + a.decay_bias[c]));
+            o[d] = lsb_to_float(row[a.r_off + c]);
+            o[a.D + d] = kd;
+            o[2 * a.D + d] = u;
+            o[3 * a.D + d] = rem * u;
+            o[4 * a.D + d] = w;
+        }
+        for (int d = lane; d < a.V; d += 32)
+            a.v_out[((size_t)t * a.H + h) * a.V + d] = lsb_to_float(row[a.v_off + (size_t)h * a.V + d]);
+    }
+}
+
+// ------------------------------------------------------------------------------ the walk
+template <int MODE>
+__global__ void __launch_bounds__(kDeltaThreads)
+delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal, const float* __restrict__ vals,
+                  float* __restrict__ state, int n_slots, const int* __restrict__ q_start,
+                  const int* __restrict__ table_rows, float* __restrict__ out, int H, int G, int D, int V, int split) {
+    constexpr int NV = MODE == 0 ? 2 : 5;          // vectors of key size a token brings
+    extern __shared__ __align__(16) float sh[];
+    const int cols = blockDim.x / split;
+    const int Dp = split * (kDeltaPer + kDeltaPad);
+    float* vec_sh = sh;                             // [chunk][NV][Dp]
+    float* val_sh = vec_sh + kDeltaChunk * NV * Dp; // [chunk][cols]
+    float* scal_sh = val_sh + kDeltaChunk * cols;   // [chunk][2]
+    lsb_pdl_launch_dependents();
+    // (channels past D are never staged: zero once, so that a lane's unused registers stay zero)
+    for (int idx = threadIdx.x; idx < kDeltaChunk * NV * Dp; idx += blockDim.x) vec_sh[idx] = 0.f;
+    lsb_pdl_wait();
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int col0 = blockIdx.x * cols;
+    const int part = threadIdx.x % split, lc = threadIdx.x / split;
+    const int col = col0 + lc;
+    const int t0 = q_start[r], t1 = q_start[r + 1];
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    const bool live = col < V;
+    float* srow = state + (((size_t)slot * H + h) * V + (live ? col : 0)) * D;
+    float s[kDeltaPer];
+#pragma unroll
+    for (int i = 0; i < kDeltaPer; ++i) {
+        const int d = part * kDeltaPer + i;
+        s[i] = (live && d < D) ? srow[d] : 0.f;
+    }
+    const int g = MODE == 0 ? h / (H / G) : 0;
+    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
+        const int n = min(kDeltaChunk, t1 - c0);
+        __syncthreads();                            // the chunk before has been walked by every lane
+        for (int idx = threadIdx.x; idx < n * NV * D; idx += blockDim.x) {
+            const int tok = idx / (NV * D), rem = idx - tok * NV * D, v = rem / D, d = rem - v * D;
+            const size_t src = MODE == 0 ? ((size_t)(c0 + tok) * 2 + v) * G * D + (size_t)g * D + d
+                                         : (((size_t)(c0 + tok) * H + h) * NV + v) * D + d;
+            vec_sh[(tok * NV + v) * Dp + (d / kDeltaPer) * (kDeltaPer + kDeltaPad) + d % kDeltaPer] = vecs[src];
+        }
+        for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
+            const int tok = idx / cols, c = idx - tok * cols;
+            val_sh[idx] = col0 + c < V ? vals[((size_t)(c0 + tok) * H + h) * V + col0 + c] : 0.f;
+        }
+        if (MODE == 0) {
+            for (int idx = threadIdx.x; idx < n * 2; idx += blockDim.x)
+                scal_sh[idx] = scal[(size_t)(c0 + idx / 2) * 2 * H + (size_t)(idx & 1) * H + h];
+        }
+        __syncthreads();
+        for (int tok = 0; tok < n; ++tok) {
+            const float* vb = vec_sh + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
+            const float v_in = val_sh[tok * cols + lc];
+            float o = 0.f;
+            if (MODE == 0) {
+                const float fade = scal_sh[tok * 2], beta = scal_sh[tok * 2 + 1];
+                const float4* q4 = reinterpret_cast<const float4*>(vb);
+                const float4* k4 = reinterpret_cast<const float4*>(vb + Dp);
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < kDeltaPer / 4; ++i) {
+                    const float4 k = k4[i];
+                    s[4 * i] *= fade; s[4 * i + 1] *= fade; s[4 * i + 2] *= fade; s[4 * i + 3] *= fade;
+                    dot += k.x * s[4 * i] + k.y * s[4 * i + 1] + k.z * s[4 * i + 2] + k.w * s[4 * i + 3];
+                }
+                for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+                const float e = beta * (v_in - dot);
+#pragma unroll
+                for (int i = 0; i < kDeltaPer / 4; ++i) {
+                    const float4 k = k4[i], q = q4[i];
+                    s[4 * i] += k.x * e; s[4 * i + 1] += k.y * e; s[4 * i + 2] += k.z * e; s[4 * i + 3] += k.w * e;
+                    o += q.x * s[4 * i] + q.y * s[4 * i + 1] + q.z * s[4 * i + 2] + q.w * s[4 * i + 3];
+                }
+            } else {
+                const float4* r4 = reinterpret_cast<const float4*>(vb);
+                const float4* k4 = reinterpret_cast<const float4*>(vb + Dp);
+                const float4* u4 = reinterpret_cast<const float4*>(vb + 2 * Dp);
+                const float4* a4 = reinterpret_cast<const float4*>(vb + 3 * Dp);
+                const float4* w4 = reinterpret_cast<const float4*>(vb + 4 * Dp);
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < kDeltaPer / 4; ++i) {
+                    const float4 u = u4[i];
+                    dot += u.x * s[4 * i] + u.y * s[4 * i + 1] + u.z * s[4 * i + 2] + u.w * s[4 * i + 3];
+                }
+                for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+#pragma unroll
+                for (int i = 0; i < kDeltaPer / 4; ++i) {
+                    const float4 k = k4[i], au = a4[i], w = w4[i], q = r4[i];
+                    s[4 * i] = w.x * s[4 * i] - au.x * dot + k.x * v_in;
+                    s[4 * i + 1] = w.y * s[4 * i + 1] - au.y * dot + k.y * v_in;
+                    s[4 * i + 2] = w.z * s[4 * i + 2] - au.z * dot + k.z * v_in;
+                    s[4 * i + 3] = w.w * s[4 * i + 3] - au.w * dot + k.w * v_in;
+                    o += q.x * s[4 * i] + q.y * s[4 * i + 1] + q.z * s[4 * i + 2] + q.w * s[4 * i + 3];
+                }
+            }
+            for (int w = split >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+            if (live && part == 0) out[((size_t)(c0 + tok) * H + h) * V + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < kDeltaPer; ++i) {
+            const int d = part * kDeltaPer + i;
+            if (d < D) srow[d] = s[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ read-out norm and gate
+// out[t, h, c] = x[t, h, c] / sqrt(mean_c x^2 + eps) * w[(h V + c) mod w_len] * act(gate[t, h V + c]);
+// gate_act 0: no gate, 1: sigmoid, 2: silu.  A warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(kDeltaThreads)
+delta_output_kernel(const float* __restrict__ x, const float* __restrict__ w, int w_len, const T* __restrict__ gate,
+                    long long gate_stride, int gate_act, T* __restrict__ out, long long pairs, int H, int V, float eps) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const long long pair = (long long)blockIdx.x * (kDeltaThreads / 32) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = pair / H;
+    const int h = (int)(pair - t * H);
+    const float* xr = x + pair * V;
+    float ss = 0.f;
+    for (int c = lane; c < V; c += 32) ss += xr[c] * xr[c];
+    const float inv = rsqrtf(lsb_warp_sum(ss) / (float)V + eps);
+    for (int c = lane; c < V; c += 32) {
+        float y = xr[c] * inv * w[(h * V + c) % w_len];
+        if (gate_act) {
+            const float z = lsb_to_float(gate[t * gate_stride + (long long)h * V + c]);
+            y *= gate_act == 1 ? delta_sigmoid(z) : z * delta_sigmoid(z);
+        }
+        out[pair * V + c] = lsb_from_float<T>(y);
+    }
+}
+
+template <typename T>
+__global__ void tanh_rows_kernel(const float* __restrict__ x, long long ld, int off, int n, T* __restrict__ out, long long count) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / n;
+        out[i] = lsb_from_float<T>(tanhf(x[t * ld + off + (i - t * n)]));
+    }
+}
+
+// -------------------------------------------------------------------------- entry points
+LSB_API int lsb_delta_max_key_dim() { return kDeltaPer * kDeltaMaxSplit; }
+
+LSB_API int lsb_gated_delta_prep(const void* proj, int dtype, long long ld, int q_off, int k_off, int v_off, int tokens,
+                                 int n_requests, int G, int H, int D, int V, int taps, const float* q_taps,
+                                 const float* k_taps, const float* v_taps, float* conv_state, int n_slots,
+                                 const float* raw, long long raw_ld, const float* a_log, const float* dt_bias,
+                                 const int* token_req, const int* q_start, const int* table_rows, float* qk_out,
+                                 float* v_out, float* scal_out, float unit_eps, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (G <= 0 || H <= 0 || H % G || D <= 0 || V <= 0 || taps < 1 || n_requests <= 0 || n_requests > 65535)
+        return (int)cudaErrorInvalidValue;
+    GatedPrepArgs a;
+    a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+    a.G = G; a.H = H; a.D = D; a.V = V; a.taps = taps;
+    a.q_taps = q_taps; a.k_taps = k_taps; a.v_taps = v_taps;
+    a.conv_state = conv_state; a.n_slots = n_slots;
+    a.raw = raw; a.raw_ld = raw_ld; a.a_log = a_log; a.dt_bias = dt_bias;
+    a.token_req = token_req; a.q_start = q_start; a.table_rows = table_rows;
+    a.qk_out = qk_out; a.v_out = v_out; a.scal_out = scal_out; a.unit_eps = unit_eps;
+    const int C = 2 * G * D + H * V;
+    const size_t smem = (size_t)C * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (smem > 48 * 1024) {
+            int rc = (int)cudaFuncSetAttribute(gated_delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (rc) return rc;
+        }
+        int rc = lsb_launch(gated_delta_prep_kernel<T>, dim3(tokens), dim3(kDeltaThreads), smem, stream, 1, a);
+        if (rc || taps == 1) return rc;
+        const int bx = (C + kDeltaThreads - 1) / kDeltaThreads;
+        return lsb_launch(conv_state_update_kernel<T>, dim3(bx > 64 ? 64 : bx, n_requests), dim3(kDeltaThreads), 0, stream, 1,
+                          (const T*)proj, ld, q_off, k_off, v_off, G * D, H * V, taps, conv_state, n_slots, q_start,
+                          table_rows);
+    });
+    return 0;
+}
+
+LSB_API int lsb_channel_delta_prep(const void* proj, int dtype, long long ld, int r_off, int k_off, int v_off, int tokens,
+                                   int H, int D, int V, const float* decay_raw, long long decay_ld, const float* decay_bias,
+                                   const float* remove_raw, long long remove_ld, const float* remove_bias,
+                                   float decay_rate, float unit_eps, float* vec_out, float* v_out, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    ChannelPrepArgs a;
+    a.proj = proj; a.ld = ld; a.r_off = r_off; a.k_off = k_off; a.v_off = v_off;
+    a.H = H; a.D = D; a.V = V;
+    a.decay_raw = decay_raw; a.decay_ld = decay_ld; a.decay_bias = decay_bias;
+    a.remove_raw = remove_raw; a.remove_ld = remove_ld; a.remove_bias = remove_bias;
+    a.decay_rate = decay_rate; a.unit_eps = unit_eps;
+    a.vec_out = vec_out; a.v_out = v_out;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(channel_delta_prep_kernel<T>, dim3(tokens), dim3(kDeltaThreads), 0, stream, 1, a));
+    return 0;
+}
+
+// mode 0: scalar gates (vecs [T, 2, G, D]: q then k; scal [T, 2, H]: fade then beta); mode 1: channel
+// gates (vecs [T, H, 5, D]: r, k, u, a * u, w).  vals [T, H, V]; state [slots, H, V, D]; out [T, H, V].
+LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const float* vals, float* state, int n_slots,
+                           const int* q_start, const int* table_rows, int n_requests, float* out, int H, int G, int D,
+                           int V, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || D > kDeltaPer * kDeltaMaxSplit || n_requests > 65535 || H > 65535 ||
+        (mode == 0 && (G <= 0 || H % G || !scal)) || (mode != 0 && mode != 1))
+        return (int)cudaErrorInvalidValue;
+    int split = 1;
+    while (split * kDeltaPer < D) split *= 2;
+    int threads = ((V * split + 31) / 32) * 32;
+    if (threads > kDeltaThreads) threads = kDeltaThreads;
+    const int cols = threads / split;
+    const int NV = mode == 0 ? 2 : 5;
+    const size_t smem = (size_t)kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
+    dim3 grid((V + cols - 1) / cols, H, n_requests);
+    int rc = 0;
+    if (mode == 0) {
+        if (smem > 48 * 1024) rc = (int)cudaFuncSetAttribute(delta_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc) return rc;
+        return lsb_launch(delta_scan_kernel<0>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, n_slots,
+                          q_start, table_rows, out, H, G, D, V, split);
+    }
+    if (smem > 48 * 1024) rc = (int)cudaFuncSetAttribute(delta_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (rc) return rc;
+    return lsb_launch(delta_scan_kernel<1>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, n_slots, q_start,
+                      table_rows, out, H, H, D, V, split);
+}
+
+LSB_API int lsb_delta_output(const float* x, const float* w, int w_len, const void* gate, long long gate_stride,
+                             int gate_act, void* out, int dtype, int tokens, int H, int V, float eps, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (H <= 0 || V <= 0 || w_len <= 0 || gate_act < 0 || gate_act > 2 || (gate_act && !gate)) return (int)cudaErrorInvalidValue;
+    const long long pairs = (long long)tokens * H;
+    const long long blocks = (pairs + kDeltaThreads / 32 - 1) / (kDeltaThreads / 32);
+    if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(delta_output_kernel<T>, dim3((unsigned)blocks), dim3(kDeltaThreads), 0, stream, 1,
+                                                x, w, w_len, (const T*)gate, gate_stride, gate_act, (T*)out, pairs, H, V, eps));
+    return 0;
+}
+
+LSB_API int lsb_tanh_rows(const float* x, long long ld, int off, int n, void* out, int dtype, int rows, cudaStream_t stream) {
+    const long long count = (long long)rows * n;
+    if (count <= 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(tanh_rows_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, 1, x, ld, off, n,
+                                                (T*)out, count));
+    return 0;
+}

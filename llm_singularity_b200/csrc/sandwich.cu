@@ -289,6 +289,42 @@ branch_mean_vec4_kernel(Branches br, float eps, T* __restrict__ out, int hidden)
 
 LSB_API int lsb_branch_max() { return kMaxBranches; }
 
+// out = sum over the branches of scale_b * y_b, summed in 32-bit (branches side by side whose results
+// are added with fixed factors, no norm).
+struct BranchScales { float s[kMaxBranches]; };
+
+template <typename T>
+__global__ void branch_sum_kernel(Branches br, BranchScales sc, T* __restrict__ out, long long count) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float s = 0.f;
+#pragma unroll
+        for (int b = 0; b < kMaxBranches; ++b)
+            if (b < br.n) s += sc.s[b] * lsb_to_float(((const T*)br.y[b])[i]);
+        out[i] = lsb_from_float<T>(s);
+    }
+}
+
+LSB_API int lsb_branch_sum(const void* const* ys, const float* scales, int n, void* out, int dtype, int n_rows, int hidden,
+                           cudaStream_t stream) {
+    const long long count = (long long)n_rows * hidden;
+    if (count <= 0) return 0;
+    if (n <= 0 || n > kMaxBranches) return (int)cudaErrorInvalidValue;
+    Branches br;
+    BranchScales sc;
+    br.n = n;
+    for (int b = 0; b < kMaxBranches; ++b) {
+        br.y[b] = b < n ? ys[b] : nullptr;
+        br.w[b] = nullptr;
+        sc.s[b] = b < n ? scales[b] : 0.f;
+    }
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(branch_sum_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, 1, br, sc, (T*)out, count));
+    return 0;
+}
+
 // ys, ws: n pointers each (rows of the branches in the compute dtype, their 32-bit weights).
 LSB_API int lsb_branch_mean(const void* const* ys, const float* const* ws, int n, float eps, void* out, int dtype,
                             int n_rows, int hidden, cudaStream_t stream) {

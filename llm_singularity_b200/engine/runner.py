@@ -23,7 +23,7 @@ from ..cache.manager import CacheManager
 from ..config.specs import ModelSpec
 from ..models.decoder import DecoderModel
 from ..parts.base import Runtime
-from ..registry import architecture_of, read_config_json
+from ..registry import architecture_of, config_of, read_config_json
 from ..weights.loader import load_checkpoint
 from .batch import ContextBuilder, StepContext, StepEntry
 
@@ -106,7 +106,7 @@ class ModelRunner:
         if config is None:
             cfg_dict = read_config_json(model_dir)
             arch = architecture_of(cfg_dict)
-            config = arch.config_cls.from_dict(cfg_dict)
+            config = config_of(model_dir, cfg_dict)
         self.config = config
         self.spec: ModelSpec = config.to_model_spec()
         self.rt = Runtime(device, self.dtype, ops=ops, page_size=page_size)

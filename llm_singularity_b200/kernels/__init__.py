@@ -1115,11 +1115,13 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
                    ctx, cache, q_out: torch.Tensor, *, q_bias=None, k_bias=None, v_bias=None, q_norm=None,
                    k_norm=None, norm_eps: float = 0.0, temp_coef: float = 0.0, temp_every: int = 0,
                    inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, pairing: str = "half",
-                   store: bool = True) -> None:
+                   store: bool = True, norm_all: bool = False, v_unit: bool = False) -> None:
     """From the rows of ``proj`` (q at ``q_off``, k at ``k_off``, v at ``v_off``) to queries in ``q_out``
     [T, nh * dk] and keys and values in this step's cache places: biases, a norm per head of q and k
     (one weight of head size each), the query temperature ``1 + coef * ln(floor((pos + 1) / every) + 1)``
-    and the rotation of the first ``rotary_dim`` dims, each if given."""
+    and the rotation of the first ``rotary_dim`` dims, each if given.  ``norm_all``: q and k are each
+    normed over all their heads at once, with weights as long as the whole projection.  ``v_unit``: every
+    value head is divided by its root mean square (eps ``norm_eps``, no weight) on its way into the cache."""
     _req(proj, "proj", dim=2)
     _req(q_out, "q_out", proj.dtype, 2)
     T, ld = proj.shape
@@ -1130,7 +1132,8 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
     if dk > _lib("attention_prep").lsb_attention_prep_max_dim():
         raise KernelError(f"attention_prep: key size {dk} is not supported")
     for name, t, n in (("q_bias", q_bias, nh * dk), ("k_bias", k_bias, nkv * dk), ("v_bias", v_bias, nkv * dv),
-                       ("q_norm", q_norm, dk), ("k_norm", k_norm, dk)):
+                       ("q_norm", q_norm, nh * dk if norm_all else dk),
+                       ("k_norm", k_norm, nkv * dk if norm_all else dk)):
         if t is not None:
             _req(t, name, torch.float32, 1)
             if t.shape[0] != n:
@@ -1140,10 +1143,12 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
         if rotary_dim % 2 or rotary_dim > dk or inv_freq.shape[0] != rotary_dim // 2:
             raise KernelError("attention_prep: rotary_dim must be even, at most the key size, with rotary_dim / 2 "
                               "frequencies")
+    if norm_all and (q_norm is None) != (k_norm is None):
+        raise KernelError("attention_prep: a norm over all heads needs both weights")
     _check_kv_cache(cache, nkv, dk, dv, proj.dtype)
     _call("attention_prep", "lsb_attention_prep", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
           _i(T), _i(nh), _i(nkv), _i(dk), _i(dv), _p(q_bias), _p(k_bias), _p(v_bias), _p(q_norm), _p(k_norm),
-          _f(norm_eps), _f(temp_coef), _i(temp_every), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
+          _f(norm_eps), _i(1 if norm_all else 0), _i(1 if v_unit else 0), _f(temp_coef), _i(temp_every), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
           _i(_PAIRINGS[pairing]), _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows), _p(cache.block_table),
           _i(cache.block_table.shape[1]), _p(q_out), _p(cache.k_pages), _p(cache.v_pages), _i(cache.page_size),
           _i(cache.k_pages.shape[0]), _i(1 if store else 0), _stream(proj))
@@ -1154,11 +1159,14 @@ DV_TENSOR_CORES = True          # bfloat16 heads of multiples of 16 up to 128 on
 
 
 def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cache, scale: float, window: int,
-                 chunk: int, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+                 chunk: int, gate: Optional[torch.Tensor], out: torch.Tensor, sink: bool = False,
+                 gate_per_head: bool = False) -> None:
     """Softmax attention of this step's queries ``q`` [T, nh * dk] over their requests' cached keys (size
     dk) and values (size dv): a query at position p sees ``[lo, p]`` with lo the larger of
     ``p - window + 1`` (window > 0) and the start of p's chunk of ``chunk`` positions (chunk > 0).
-    ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate).
+    ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate); with ``gate_per_head`` it is
+    [T, nh], one number per head.  ``sink``: one is added to the softmax's denominator (a place with
+    score 0 and no value).
 
     bfloat16 with both sizes multiples of 16 up to 128 runs on the tensor cores (prompt portions in
     tiles of 64 rows, a row being a position and a head of a kv head's group; single tokens with the
@@ -1175,9 +1183,10 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
     gate_stride = 0
     if gate is not None:
         _req(gate, "gate", q.dtype, 2, contiguous=False)
-        if gate.shape != (T, nh * dv) or gate.stride(1) != 1:
-            raise KernelError("attention_dv: the gate must be [T, heads * value size] with unit column stride")
+        if gate.shape != (T, nh if gate_per_head else nh * dv) or gate.stride(1) != 1:
+            raise KernelError("attention_dv: the gate must be [T, heads * value size] (or [T, heads]) with unit column stride")
         gate_stride = gate.stride(0)
+    flags = (1 if sink else 0) | (2 if gate is not None and gate_per_head else 0)
     _check_kv_cache(cache, nkv, dk, dv, q.dtype)
     if (DV_TENSOR_CORES and q.dtype == torch.bfloat16 and gate_stride % 2 == 0
             and (gate is None or gate.data_ptr() % 4 == 0)
@@ -1198,12 +1207,193 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
               _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
               _ll(gate_stride), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(dv),
               _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(num_sms(q.device)),
-              _i(DV_BLOCK_SHAPE), _p(scratch), _stream(out))
+              _i(DV_BLOCK_SHAPE), _p(scratch), _i(flags), _stream(out))
         return
     _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
           _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
           _ll(gate_stride), _p(out), _i(_dt(q)), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),
-          _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _stream(out))
+          _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(flags), _stream(out))
+
+
+def branch_sum(ys, scales, out: torch.Tensor) -> None:
+    """out = sum_b scales[b] * ys[b], summed in 32-bit (mixers side by side whose results are added
+    with fixed factors)."""
+    n = len(ys)
+    if n == 0 or len(scales) != n:
+        raise KernelError("branch_sum: one factor per branch")
+    _req(out, "out", dim=2)
+    for y in ys:
+        _req(y, "branch", out.dtype, 2)
+        if y.shape != out.shape:
+            raise KernelError("branch_sum: every branch must have out's shape")
+    yp = (ctypes.c_void_p * n)(*[_p(y).value for y in ys])
+    sc = (ctypes.c_float * n)(*[float(x) for x in scales])
+    _call("sandwich", "lsb_branch_sum", yp, sc, _i(n), _p(out), _i(_dt(out)), _i(out.shape[0]), _i(out.shape[1]),
+          _stream(out))
+
+
+PLAIN_ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3, "bent_square": 4}
+
+
+def plain_activation(x: torch.Tensor, out: torch.Tensor, activation: str, c_pos: float = 0.0, c_neg: float = 0.0) -> None:
+    """out = act(x) element by element, evaluated in 32-bit.  "bent_square": ``c_pos z^2 + z/2`` right of
+    zero, ``c_neg (e^z - 1 - z) + z/2`` left of it."""
+    _req(x, "x")
+    _req(out, "out", x.dtype)
+    if out.shape != x.shape or activation not in PLAIN_ACTIVATIONS:
+        raise KernelError(f"plain_activation: shapes disagree or '{activation}' is not known")
+    _call("activation", "lsb_plain_act", _p(x), _p(out), _i(_dt(x)), _ll(x.numel()), _i(PLAIN_ACTIVATIONS[activation]),
+          _f(c_pos), _f(c_neg), _stream(out))
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (32-bit)."""
+    _req(x, "x", torch.float32)
+    if not cap > 0:
+        raise KernelError("softcap: the cap must be positive")
+    _call("activation", "lsb_softcap", _p(x), _ll(x.numel()), _f(cap), _stream(x))
+
+
+# ---------------------------------------------------------------------- delta-rule memories
+def delta_max_key_dim() -> int:
+    return int(_lib("delta_rule").lsb_delta_max_key_dim())
+
+
+def gated_delta_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, key_heads: int, heads: int, key_dim: int,
+                     value_dim: int, taps, conv_state: Optional[torch.Tensor], raw: torch.Tensor, a_log: torch.Tensor,
+                     dt_bias: torch.Tensor, ctx, qk: torch.Tensor, v: torch.Tensor, scal: torch.Tensor,
+                     unit_eps: float = 1e-6) -> None:
+    """What a delta-rule memory with scalar gates needs of a step's tokens, in 32-bit.  ``proj`` [T, columns]
+    holds the projections of q and k (``key_heads * key_dim`` each) and v (``heads * value_dim``); ``taps`` =
+    (q, k, v) filters [channels, n] of a causal convolution over time whose last column meets the current
+    token, the n - 1 inputs before a portion coming from ``conv_state`` [slots, n - 1, channels] (updated
+    for the next step); then silu; q and k to unit length per head, q also times key_dim^-1/2 -> ``qk``
+    [T, 2 * key_heads * key_dim]; v -> ``v`` [T, heads * value_dim].  ``raw`` [T, 2 * heads] 32-bit: the
+    projections of beta and of the fade; ``scal`` [T, 2 * heads] receives
+    exp(-exp(a_log) * softplus(. + dt_bias)) and then sigmoid(.)."""
+    _req(proj, "proj", dim=2)
+    T, ld = proj.shape
+    GD, HV = key_heads * key_dim, heads * value_dim
+    C = 2 * GD + HV
+    n = taps[0].shape[1]
+    for name, t, rows in (("q taps", taps[0], GD), ("k taps", taps[1], GD), ("v taps", taps[2], HV)):
+        _req(t, name, torch.float32, 2)
+        if t.shape != (rows, n):
+            raise KernelError(f"gated_delta_prep: {name} must be [{rows}, {n}]")
+    if n > 1:
+        _req(conv_state, "conv_state", torch.float32, 3)
+        if conv_state.shape[1:] != (n - 1, C):
+            raise KernelError(f"gated_delta_prep: conv_state must be [slots, {n - 1}, {C}]")
+    _req(raw, "raw", torch.float32, 2, contiguous=False)
+    for name, t, shape in (("qk", qk, (T, 2 * GD)), ("v", v, (T, HV)), ("scal", scal, (T, 2 * heads))):
+        _req(t, name, torch.float32, 2)
+        if t.shape != shape:
+            raise KernelError(f"gated_delta_prep: {name} must be {shape}")
+    for name, t in (("a_log", a_log), ("dt_bias", dt_bias)):
+        _req(t, name, torch.float32, 1)
+        if t.shape[0] != heads:
+            raise KernelError(f"gated_delta_prep: {name} must have {heads} entries")
+    if (ctx.n_tokens != T or raw.shape != (T, 2 * heads) or raw.stride(1) != 1 or min(q_off, k_off, v_off) < 0
+            or max(q_off, k_off) + GD > ld or v_off + HV > ld or heads % key_heads):
+        raise KernelError("gated_delta_prep: proj, raw and the step do not fit the sizes")
+    _call("delta_rule", "lsb_gated_delta_prep", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off), _i(T),
+          _i(ctx.n_requests), _i(key_heads), _i(heads), _i(key_dim), _i(value_dim), _i(n), _p(taps[0]), _p(taps[1]),
+          _p(taps[2]), _p(conv_state if n > 1 else None), _i(conv_state.shape[0] if n > 1 else 1 << 30), _p(raw),
+          _ll(raw.stride(0)), _p(a_log), _p(dt_bias), _p(ctx.token_req), _p(ctx.q_start), _p(ctx.table_rows), _p(qk), _p(v),
+          _p(scal), _f(unit_eps), _stream(proj))
+
+
+def channel_delta_prep(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int, key_dim: int, value_dim: int,
+                       decay_raw: torch.Tensor, decay_bias: torch.Tensor, remove_raw: torch.Tensor,
+                       remove_bias: torch.Tensor, decay_rate: float, vecs: torch.Tensor, v: torch.Tensor,
+                       unit_eps: float = 1e-6) -> None:
+    """What a delta-rule memory with a gate per key channel needs, in 32-bit: per token and head the read
+    vector r, the key k, its unit vector u = k / sqrt(sum k^2 + eps), a * u with a = sigmoid(remove_raw +
+    remove_bias) and the decay w = exp(-decay_rate * sigmoid(decay_raw + decay_bias)) -> ``vecs``
+    [T, heads, 5, key_dim]; the values -> ``v`` [T, heads * value_dim]."""
+    _req(proj, "proj", dim=2)
+    T, ld = proj.shape
+    HD = heads * key_dim
+    for name, t in (("decay_raw", decay_raw), ("remove_raw", remove_raw)):
+        _req(t, name, torch.float32, 2, contiguous=False)
+        if t.shape != (T, HD) or t.stride(1) != 1:
+            raise KernelError(f"channel_delta_prep: {name} must be [T, heads * key_dim] with unit column stride")
+    for name, t in (("decay_bias", decay_bias), ("remove_bias", remove_bias)):
+        _req(t, name, torch.float32, 1)
+        if t.shape[0] != HD:
+            raise KernelError(f"channel_delta_prep: {name} must have {HD} entries")
+    _req(vecs, "vecs", torch.float32, 4)
+    _req(v, "v", torch.float32, 2)
+    if (vecs.shape != (T, heads, 5, key_dim) or v.shape != (T, heads * value_dim) or min(r_off, k_off, v_off) < 0
+            or max(r_off, k_off) + HD > ld or v_off + heads * value_dim > ld):
+        raise KernelError("channel_delta_prep: proj, vecs and v do not fit the sizes")
+    _call("delta_rule", "lsb_channel_delta_prep", _p(proj), _i(_dt(proj)), _ll(ld), _i(r_off), _i(k_off), _i(v_off), _i(T),
+          _i(heads), _i(key_dim), _i(value_dim), _p(decay_raw), _ll(decay_raw.stride(0)), _p(decay_bias), _p(remove_raw),
+          _ll(remove_raw.stride(0)), _p(remove_bias), _f(decay_rate), _f(unit_eps), _p(vecs), _p(v), _stream(proj))
+
+
+def delta_scan(form: str, vecs: torch.Tensor, scal: Optional[torch.Tensor], vals: torch.Tensor, state: torch.Tensor, ctx,
+               out: torch.Tensor, heads: int, key_heads: int, key_dim: int, value_dim: int) -> None:
+    """The walk of a delta-rule memory, each request from its slot's state (``state`` [slots, heads,
+    value_dim, key_dim] 32-bit, updated in place), tokens in order; ``out`` [T, heads * value_dim] 32-bit.
+    "scalar": S <- g S; e = beta (v - S^T k); S += k e^T; o = S^T q, with ``vecs`` [T, 2 * key_heads * key_dim]
+    (q then k) and ``scal`` [T, 2 * heads] (g then beta).  "channel": S <- diag(w) S - (a * u)(u^T S) + k v^T,
+    o = S^T r, with ``vecs`` [T, heads, 5, key_dim] (r, k, u, a * u, w)."""
+    if form not in ("scalar", "channel"):
+        raise KernelError(f"delta_scan: form '{form}' is not known (scalar, channel)")
+    _req(vecs, "vecs", torch.float32)
+    _req(vals, "vals", torch.float32, 2)
+    _req(state, "state", torch.float32, 4)
+    _req(out, "out", torch.float32, 2)
+    T = vals.shape[0]
+    n_vec = 2 * key_heads * key_dim if form == "scalar" else heads * 5 * key_dim
+    if (state.shape[1:] != (heads, value_dim, key_dim) or out.shape != (T, heads * value_dim) or vals.shape != out.shape
+            or ctx.n_tokens != T or vecs.numel() != T * n_vec):
+        raise KernelError("delta_scan: vecs, vals, state, out or the step do not fit the sizes")
+    if form == "scalar":
+        _req(scal, "scal", torch.float32, 2)
+        if scal.shape != (T, 2 * heads) or heads % key_heads:
+            raise KernelError("delta_scan: scal must be [T, 2 * heads]")
+    if key_dim > delta_max_key_dim():
+        raise KernelError(f"delta_scan: key_dim {key_dim} is not supported (at most {delta_max_key_dim()})")
+    _call("delta_rule", "lsb_delta_scan", _i(0 if form == "scalar" else 1), _p(vecs), _p(scal if form == "scalar" else None),
+          _p(vals), _p(state), _i(state.shape[0]), _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out),
+          _i(heads), _i(key_heads), _i(key_dim), _i(value_dim), _stream(out))
+
+
+_DELTA_GATES = {"none": 0, "sigmoid": 1, "silu": 2}
+
+
+def delta_output(x: torch.Tensor, weight: torch.Tensor, heads: int, eps: float, gate: Optional[torch.Tensor],
+                 gate_act: str, out: torch.Tensor) -> None:
+    """out = each head of the 32-bit row ``x`` [T, heads * V] divided by its root mean square, times ``weight``
+    (its index taken modulo its length: one weight per head, or one over the row), times sigmoid or silu of
+    ``gate`` [T, heads * V] (rows may be strided)."""
+    _req(x, "x", torch.float32, 2)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, n = x.shape
+    if out.shape != (T, n) or heads <= 0 or n % heads or n % weight.shape[0] or gate_act not in _DELTA_GATES:
+        raise KernelError("delta_output: shapes disagree")
+    gate_stride = 0
+    if gate is not None:
+        _req(gate, "gate", out.dtype, 2, contiguous=False)
+        if gate.shape != (T, n) or gate.stride(1) != 1:
+            raise KernelError("delta_output: the gate must have x's shape and unit column stride")
+        gate_stride = gate.stride(0)
+    _call("delta_rule", "lsb_delta_output", _p(x), _p(weight), _i(weight.shape[0]), _p(gate), _ll(gate_stride),
+          _i(_DELTA_GATES[gate_act] if gate is not None else 0), _p(out), _i(_dt(out)), _i(T), _i(heads), _i(n // heads),
+          _f(eps), _stream(out))
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x) in the compute dtype; ``x`` 32-bit [T, n], rows may be strided."""
+    _req(x, "x", torch.float32, 2, contiguous=False)
+    _req(out, "out", dim=2)
+    if out.shape != x.shape or x.stride(1) != 1:
+        raise KernelError("tanh_rows: shapes disagree")
+    _call("delta_rule", "lsb_tanh_rows", _p(x), _ll(x.stride(0)), _i(0), _i(x.shape[1]), _p(out), _i(_dt(out)),
+          _i(x.shape[0]), _stream(out))
 
 
 # -------------------------------------------------- matrix memory with an exponential input gate

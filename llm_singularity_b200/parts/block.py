@@ -26,12 +26,14 @@ class PreNormBlock(Part):
         super().__init__(spec, rt)
         self.mixer_norm = NORMS.build(spec.mixer_norm, rt)
         self.mixer = MIXERS.build(spec.mixer, rt)
-        self.ffn_norm = NORMS.build(spec.ffn_norm, rt)
-        self.ffn = FEED_FORWARDS.build(spec.ffn, rt)
+        self.ffn_norm = NORMS.build(spec.ffn_norm, rt) if spec.ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(spec.ffn, rt) if spec.ffn is not None else None
 
     def children(self) -> Dict[str, Part]:
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
-                "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+        c = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            c.update(ffn_norm=self.ffn_norm, ffn=self.ffn)
+        return c
 
     def first_norm(self):
         """The norm this block's input meets first, if the block before may fold it into its last
@@ -58,6 +60,12 @@ class PreNormBlock(Part):
             h = pending
         else:
             h = self.mixer_norm.add_norm(residual, pending)
+        if self.ffn is None:
+            # the mixer's result is the block's: the norm it meets next is the next block's or the head's
+            if fold and next_norm is not None and self.mixer.folds_norm:
+                return self.mixer.forward(self._input(h, self.mixer), ctx, cache, writes_cache,
+                                          into=(residual, *next_norm.fold()))
+            return self.mixer.forward(self._input(h, self.mixer), ctx, cache, writes_cache)
         if fold and self.mixer.folds_norm and self.ffn_norm.foldable:
             h = self.mixer.forward(self._input(h, self.mixer), ctx, cache, writes_cache,
                                    into=(residual, *self.ffn_norm.fold()))

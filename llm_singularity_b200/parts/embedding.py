@@ -73,6 +73,8 @@ class LMHead(Part):
         super().__init__(spec, rt)
         self.norm = NORMS.build(spec.norm, rt)
         self.weight: Optional[torch.Tensor] = None
+        if getattr(spec, "logit_softcap", None):
+            self.kernels = self.kernels + ("activation",)
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
@@ -93,4 +95,8 @@ class LMHead(Part):
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor],
                 rows: torch.Tensor) -> torch.Tensor:
         h = self.norm.gather_add_norm(residual, pending, rows)
-        return self.rt.ops.linear(h, self.weight, out_dtype=torch.float32)
+        logits = self.rt.ops.linear(h, self.weight, out_dtype=torch.float32)
+        cap = getattr(self.spec, "logit_softcap", None)
+        if cap:
+            self.rt.ops.softcap(logits, float(cap))           # cap * tanh(logits / cap), in place
+        return logits

@@ -7,7 +7,10 @@ keys and values to this step's cache places -> every query row attends the cache
 it, within its window and its chunk, query head ``h`` reading kv head ``h // (heads / kv_heads)``
 -> the heads' outputs times ``sigmoid(Wg x)`` -> output projection.  Each of bias, norm,
 temperature, rotation, window, chunk and gate is there only if the spec asks for it.  Scores,
-softmax, norms, positions and angles are 32-bit.
+softmax, norms, positions and angles are 32-bit.  Further options of the spec: the norm of q and k
+taken over all heads at once (``qk_norm_span`` "all"), value heads brought to unit rms before they
+are cached (``v_unit_norm``), one more place with score 0 and no value in every softmax (``sink``),
+and a gate of one number per head (``gate_per_head``).
 
 Where the spec is what the framework's grouped attention already covers after the preparation (keys
 and values of one size, no chunks, no gate), the same attention kernels run (tensor cores for
@@ -37,6 +40,12 @@ class KVAttention(Part):
                 raise ValueError(f"{name} must be at least 1, got {v}")
         if s.temp_every < 0:
             raise ValueError(f"temp_every must not be negative, got {s.temp_every}")
+        self.norm_all = getattr(s, "qk_norm_span", "head") == "all"
+        if getattr(s, "qk_norm_span", "head") not in ("head", "all"):
+            raise ValueError(f"qk_norm_span '{s.qk_norm_span}' is not known (head, all)")
+        self.v_unit = bool(getattr(s, "v_unit_norm", False))
+        self.sink = bool(getattr(s, "sink", False))
+        self.gate_per_head = bool(getattr(s, "gate_per_head", False))
         self.position = POSITIONS.build(s.position, rt)
         self.table = self.position.rotary_table()
         if self.table is None and s.position.kind != "none":
@@ -48,7 +57,7 @@ class KVAttention(Part):
         self.o_size = s.num_heads * s.value_dim
         # the framework's grouped attention takes over where nothing here is beyond it
         self.plain = (s.key_dim == s.value_dim and s.chunk is None and not s.out_gate and s.key_dim % 16 == 0
-                      and 16 <= s.key_dim <= 256)
+                      and 16 <= s.key_dim <= 256 and not self.sink)
         if self.plain:
             self.kernels = self.kernels + ("attention",)
             if rt.dtype == torch.bfloat16 and s.key_dim in (64, 128):
@@ -65,10 +74,11 @@ class KVAttention(Part):
                      k_bias=ParamSpec((k,), role="vector", init="normal"),
                      v_bias=ParamSpec((v,), role="vector", init="normal"))
         if s.qk_norm:
-            p.update(q_norm=ParamSpec((s.key_dim,), role="vector", init="ones"),
-                     k_norm=ParamSpec((s.key_dim,), role="vector", init="ones"))
+            whole = getattr(s, "qk_norm_span", "head") == "all"
+            p.update(q_norm=ParamSpec((q if whole else s.key_dim,), role="vector", init="ones"),
+                     k_norm=ParamSpec((k if whole else s.key_dim,), role="vector", init="ones"))
         if s.out_gate:
-            p["g"] = ParamSpec((o, H))
+            p["g"] = ParamSpec((s.num_heads if getattr(s, "gate_per_head", False) else o, H))
         return p
 
     def children(self):
@@ -94,12 +104,29 @@ class KVAttention(Part):
         ops.attention_prep(proj, 0, self.q_size, self.q_size + self.k_size, s.num_heads, s.num_kv_heads,
                            s.key_dim, s.value_dim, ctx, cache, q, norm_eps=s.eps, temp_coef=s.temp_coef,
                            temp_every=s.temp_every, inv_freq=inv_freq, rotary_dim=rotary_dim, pairing=self.pairing,
-                           store=writes_cache, **self.extras)
+                           store=writes_cache, **self.extras, **self._prep_options())
         out = self.rt.empty(T, self.o_size)
         if self.plain:
             ops.paged_attention(q, s.num_heads, s.num_kv_heads, s.key_dim, ctx, cache, s.scale, s.window or 0, out)
         else:
             gate = proj[:, self.q_size + self.k_size + self.v_size:] if s.out_gate else None
             ops.attention_dv(q, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, ctx, cache, s.scale,
-                             s.window or 0, s.chunk or 0, gate, out)
+                             s.window or 0, s.chunk or 0, gate, out, **self._softmax_options())
         return ops.linear(out, self.w_out)
+
+    def _prep_options(self) -> dict:
+        """Keyword arguments of the preparation kernel that only some specs need."""
+        opts = {}
+        if self.norm_all:
+            opts["norm_all"] = True
+        if self.v_unit:
+            opts["v_unit"] = True
+        return opts
+
+    def _softmax_options(self) -> dict:
+        opts = {}
+        if self.sink:
+            opts["sink"] = True
+        if self.gate_per_head and self.spec.out_gate:
+            opts["gate_per_head"] = True
+        return opts

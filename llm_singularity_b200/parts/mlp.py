@@ -17,6 +17,47 @@ import torch
 from .base import ParamSpec, Part, register_feed_forward
 
 
+@register_feed_forward("dense_mlp")
+class DenseMLP(Part):
+    """``down(act(up(x)))``: two products with an activation between them, no gate and no bias.  The
+    activation is named by the spec; "bent_square" has two learnt numbers p and q (``act`` [2]):
+    ``softplus(p) z^2 + z/2`` right of zero, ``(1/2 + softplus(q)) (e^z - 1 - z) + z/2`` left of it.  The
+    two factors are formed once at load, in 64-bit; the activation itself is evaluated in 32-bit."""
+
+    graph_safe = True
+    replayable = True
+    kernels = ("gemm", "activation")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        known = getattr(rt.ops, "PLAIN_ACTIVATIONS", None)
+        if known is not None and spec.activation not in known:
+            raise ValueError(f"activation '{spec.activation}' is not implemented (known: {', '.join(sorted(known))})")
+        self.c_pos = self.c_neg = 0.0
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        H, I = spec.hidden_size, spec.intermediate_size
+        p = {"up_proj": ParamSpec((I, H)), "down_proj": ParamSpec((H, I))}
+        if spec.activation == "bent_square":
+            p["act"] = ParamSpec((2,), role="vector", init="normal")
+        return p
+
+    def load(self, tensors):
+        self.w_up = tensors["up_proj"].contiguous()
+        self.w_down = tensors["down_proj"].contiguous()
+        if "act" in tensors:
+            pq = torch.nn.functional.softplus(tensors["act"].detach().to("cpu", torch.float64))
+            self.c_pos, self.c_neg = float(pq[0]), 0.5 + float(pq[1])
+
+    def forward(self, x, ctx, into=None):
+        ops = self.rt.ops
+        z = ops.linear(x, self.w_up)
+        a = self.rt.empty(*z.shape)
+        ops.plain_activation(z, a, self.spec.activation, self.c_pos, self.c_neg)
+        return ops.linear(a, self.w_down)
+
+
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
     graph_safe = True

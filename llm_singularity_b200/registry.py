@@ -66,10 +66,40 @@ def architecture_of(config_dict: dict) -> Architecture:
     return get_architecture(archs[0])
 
 
+def checkpoint_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor in the folder's safetensors files (headers only); empty if the
+    folder has none."""
+    from .weights.loader import checkpoint_files
+    from .weights.safetensors_io import SafetensorsFile
+    shapes: Dict[str, tuple] = {}
+    try:
+        files = checkpoint_files(model_dir)
+    except FileNotFoundError:
+        return shapes
+    for path in files:
+        f = SafetensorsFile(path)
+        for name in f.names():
+            shapes[name] = tuple(f.info(name)[1])
+    return shapes
+
+
+def config_of(model_dir: str, d: Optional[dict] = None):
+    """The typed configuration of the model in ``model_dir``.  A size that no key of config.json
+    gives but a stored tensor's shape does is taken from the checkpoint, by configurations that have
+    ``with_checkpoint_shapes``."""
+    d = read_config_json(model_dir) if d is None else d
+    config = architecture_of(d).config_cls.from_dict(d)
+    fill = getattr(config, "with_checkpoint_shapes", None)
+    if fill is not None:
+        shapes = checkpoint_shapes(model_dir)
+        if shapes:
+            config = fill(shapes)
+    return config
+
+
 def load_config(model_dir: str):
     """Parse ``<model_dir>/config.json`` into the typed configuration of its architecture."""
-    d = read_config_json(model_dir)
-    return architecture_of(d).config_cls.from_dict(d)
+    return config_of(model_dir)
 
 
 def _register_builtin() -> None:
@@ -79,6 +109,8 @@ def _register_builtin() -> None:
     register_architecture(RidotarConfig.architecture, RidotarConfig)
     from .config.fogezen import FogezenConfig
     register_architecture(FogezenConfig.architecture, FogezenConfig)
+    from .config.fikizen import FikizenConfig
+    register_architecture(FikizenConfig.architecture, FikizenConfig)
 
 
 _register_builtin()
