@@ -1,4 +1,10 @@
-"""Prefill and decode throughput of a design (Ridotar, Fogezen) beside the Llama decoder at equal size.
+"""Prefill and decode throughput of a design (Ridotar, Fogezen, Fikizen) beside the Llama decoder at equal size.
+
+Fikizen: layers cycling through windowed sink attention with a gate per head, the gated
+delta-rule memory behind short convolutions (no feed-forward), the parallel pair (normed windowed
+attention beside the delta-rule memory with gates per key channel) and the first layer's weights
+once more; dense ungated feed-forwards of the Llama model's width.  It is also run beside Fogezen,
+the design closest to it (mixers side by side, a matrix memory, attention with sizes of its own).
 
 Fogezen: layers alternating between biased attention with a query temperature and the parallel
 pair (chunked, gated attention with normed and rotated heads beside a matrix memory), the second
@@ -66,7 +72,33 @@ def fogezen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
             "loop": {"start": 1, "stop": 2, "times": 2 if layers > 2 else 1}}
 
 
-DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config}
+def fikizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
+    heads = width // 128
+    mlp = {"kind": "dense", "ff": top * ff}
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": 1024}, "rot": {"base": 1000000.0, "dims": 64}}
+    delta = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}
+    pair = {"left": {"heads": max(1, heads // 2), "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 64,
+                     "scale": 128 ** -0.5, "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}},
+            "right": {"heads": max(1, heads // 2), "dim": 64}, "left_scale": 0.6, "right_scale": 0.5}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            out.append({"type": "attention", "mixer": dict(attention), "mlp": mlp})
+        elif kind == 1:
+            out.append({"type": "delta", "mixer": dict(delta), "mlp": None})
+        elif kind == 2:
+            out.append({"type": "parallel", "mixer": dict(pair), "mlp": mlp})
+        else:
+            out.append({"type": "attention", "mixer": dict(attention), "mlp": mlp, "weights_of": 0})
+    return {"architecture": "Fikizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": out}
+
+
+DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config, "fikizen": fikizen_config}
+# the designs each is also measured beside (Llama always is)
+CLOSEST = {"fikizen": ("fogezen",)}
 
 
 def llama_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
@@ -151,11 +183,15 @@ def compare(sizes=("w1024", "w2048"), prefill_tokens=2048, batch=8, context=2048
         if layers:
             size["layers"] = layers
         row = {"size": size}
-        for which, make in ((design, DESIGNS[design]), ("llama", llama_config)):
+        others = [(d, DESIGNS[d]) for d in CLOSEST.get(design, ())]
+        for which, make in [(design, DESIGNS[design])] + others + [("llama", llama_config)]:
             row[which] = _measure(make(**size), size["vocab"], prefill_tokens, batch, context, steps, warmup, reps)
             gc.collect()
             torch.cuda.empty_cache()
         row[design + "_over_llama"] = {"prefill": round(row[design]["prefill_tok_s"] / row["llama"]["prefill_tok_s"], 3),
                                        "decode": round(row[design]["decode_tok_s"] / row["llama"]["decode_tok_s"], 3)}
+        for d, _ in others:
+            row[design + "_over_" + d] = {"prefill": round(row[design]["prefill_tok_s"] / row[d]["prefill_tok_s"], 3),
+                                          "decode": round(row[design]["decode_tok_s"] / row[d]["decode_tok_s"], 3)}
         out[name] = row
     return out
