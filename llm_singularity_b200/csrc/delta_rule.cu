@@ -28,6 +28,14 @@
 // order, so the result does not depend on how a prompt was cut.  A column's key channels are dealt to
 // `split` neighbouring lanes, 32 each, kept in registers; dots are finished by shuffles.  The tokens'
 // vectors come through shared memory in chunks of 16 tokens.
+//
+// Long portions are cut into segments that are walked side by side, since a walk is a chain of
+// dependent steps and one portion alone gives the chip few of them.  A token's step is linear in the
+// state, S <- A_t S + k x^T with A_t = g (I - beta k k^T) or diag(w) - (a * u) u^T, so a segment walked
+// from nothing gives its own contribution E, and the identity's columns walked through the same steps
+// (with nothing written) give the product P of its transitions; a small kernel chains the segments,
+// start(s + 1) = P_s start(s) + E_s; every segment is then walked again from its start for the outputs.
+// The sums form in another order than in one walk: equal beyond rounding.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
@@ -168,11 +176,21 @@ __global__ void __launch_bounds__(kDeltaThreads) channel_delta_prep_kernel(Chann
 }
 
 // ------------------------------------------------------------------------------ the walk
-template <int MODE>
+// SEG 0: a request's whole portion from its slot's state, outputs, the slot's state left behind.
+// SEG 1: one segment of a portion from nothing: the V value columns start at zero and gather what the
+//        segment's tokens write (E); D more columns start as the identity and take no writes, which
+//        leaves the product P of the segment's transitions (a token's step is linear in the state:
+//        S <- A_t S + k x^T, and a column of the identity walks through the same steps with x = 0).
+//        No outputs; E and P go to seg_acc [request * max_segs + segment, head, V + D, D].
+// SEG 2: one segment from its start state (seg_start, laid out like the state), outputs only.
+// Between 1 and 2 delta_chain_kernel forms start(s + 1) = P_s start(s) + E_s segment after segment.
+// Three times the arithmetic of one walk, a chain a segment long.
+template <int MODE, int SEG>
 __global__ void __launch_bounds__(kDeltaThreads)
 delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal, const float* __restrict__ vals,
                   float* __restrict__ state, int n_slots, const int* __restrict__ q_start,
-                  const int* __restrict__ table_rows, float* __restrict__ out, int H, int G, int D, int V, int split) {
+                  const int* __restrict__ table_rows, float* __restrict__ out, int H, int G, int D, int V, int split,
+                  int seg_len, int max_segs, float* __restrict__ seg_acc, const float* __restrict__ seg_start) {
     constexpr int NV = MODE == 0 ? 2 : 5;          // vectors of key size a token brings
     extern __shared__ __align__(16) float sh[];
     const int cols = blockDim.x / split;
@@ -184,23 +202,33 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     // (channels past D are never staged: zero once, so that a lane's unused registers stay zero)
     for (int idx = threadIdx.x; idx < kDeltaChunk * NV * Dp; idx += blockDim.x) vec_sh[idx] = 0.f;
     lsb_pdl_wait();
-    const int r = blockIdx.z, h = blockIdx.y;
+    const int r = SEG ? blockIdx.z / max_segs : blockIdx.z, sidx = SEG ? blockIdx.z % max_segs : 0;
+    const int h = blockIdx.y;
     const int col0 = blockIdx.x * cols;
     const int part = threadIdx.x % split, lc = threadIdx.x / split;
     const int col = col0 + lc;
-    const int t0 = q_start[r], t1 = q_start[r + 1];
+    const int Vs = SEG == 1 ? V + D : V;            // columns walked
+    int t0 = q_start[r], t1 = q_start[r + 1];
+    if (SEG) {
+        t0 += sidx * seg_len;
+        if (t0 >= t1) return;                       // the request has fewer segments
+        t1 = min(t1, t0 + seg_len);
+    }
     const int slot = table_rows[r];
     if (slot < 0 || slot >= n_slots) {
         if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
         return;
     }
-    const bool live = col < V;
-    float* srow = state + (((size_t)slot * H + h) * V + (live ? col : 0)) * D;
+    const bool live = col < Vs;
+    float* srow = SEG == 1 ? seg_acc + (((size_t)blockIdx.z * H + h) * Vs + (live ? col : 0)) * D
+                           : state + (((size_t)slot * H + h) * V + (live ? col : 0)) * D;
+    const float* first = SEG == 2 ? seg_start + (((size_t)blockIdx.z * H + h) * V + (live ? col : 0)) * D : srow;
     float s[kDeltaPer];
 #pragma unroll
     for (int i = 0; i < kDeltaPer; ++i) {
         const int d = part * kDeltaPer + i;
-        s[i] = (live && d < D) ? srow[d] : 0.f;
+        if (SEG == 1) s[i] = (live && col >= V && d == col - V) ? 1.f : 0.f;
+        else s[i] = (live && d < D) ? first[d] : 0.f;
     }
     const int g = MODE == 0 ? h / (H / G) : 0;
     for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
@@ -224,25 +252,31 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
         for (int tok = 0; tok < n; ++tok) {
             const float* vb = vec_sh + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
             const float v_in = val_sh[tok * cols + lc];
-            float o = 0.f;
+            // (dots gather in four partial sums, so that a token's chain of dependent additions is a
+            // quarter as long; every walk sums in this same order)
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
             if (MODE == 0) {
                 const float fade = scal_sh[tok * 2], beta = scal_sh[tok * 2 + 1];
                 const float4* q4 = reinterpret_cast<const float4*>(vb);
                 const float4* k4 = reinterpret_cast<const float4*>(vb + Dp);
-                float dot = 0.f;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 k = k4[i];
                     s[4 * i] *= fade; s[4 * i + 1] *= fade; s[4 * i + 2] *= fade; s[4 * i + 3] *= fade;
-                    dot += k.x * s[4 * i] + k.y * s[4 * i + 1] + k.z * s[4 * i + 2] + k.w * s[4 * i + 3];
+                    d0 += k.x * s[4 * i]; d1 += k.y * s[4 * i + 1]; d2 += k.z * s[4 * i + 2]; d3 += k.w * s[4 * i + 3];
                 }
+                float dot = (d0 + d1) + (d2 + d3);
                 for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
                 const float e = beta * (v_in - dot);
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
-                    const float4 k = k4[i], q = q4[i];
+                    const float4 k = k4[i];
                     s[4 * i] += k.x * e; s[4 * i + 1] += k.y * e; s[4 * i + 2] += k.z * e; s[4 * i + 3] += k.w * e;
-                    o += q.x * s[4 * i] + q.y * s[4 * i + 1] + q.z * s[4 * i + 2] + q.w * s[4 * i + 3];
+                    if (SEG != 1) {
+                        const float4 q = q4[i];
+                        o0 += q.x * s[4 * i]; o1 += q.y * s[4 * i + 1]; o2 += q.z * s[4 * i + 2]; o3 += q.w * s[4 * i + 3];
+                    }
                 }
             } else {
                 const float4* r4 = reinterpret_cast<const float4*>(vb);
@@ -250,33 +284,102 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
                 const float4* u4 = reinterpret_cast<const float4*>(vb + 2 * Dp);
                 const float4* a4 = reinterpret_cast<const float4*>(vb + 3 * Dp);
                 const float4* w4 = reinterpret_cast<const float4*>(vb + 4 * Dp);
-                float dot = 0.f;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 u = u4[i];
-                    dot += u.x * s[4 * i] + u.y * s[4 * i + 1] + u.z * s[4 * i + 2] + u.w * s[4 * i + 3];
+                    d0 += u.x * s[4 * i]; d1 += u.y * s[4 * i + 1]; d2 += u.z * s[4 * i + 2]; d3 += u.w * s[4 * i + 3];
                 }
+                float dot = (d0 + d1) + (d2 + d3);
                 for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
-                    const float4 k = k4[i], au = a4[i], w = w4[i], q = r4[i];
+                    const float4 k = k4[i], au = a4[i], w = w4[i];
                     s[4 * i] = w.x * s[4 * i] - au.x * dot + k.x * v_in;
                     s[4 * i + 1] = w.y * s[4 * i + 1] - au.y * dot + k.y * v_in;
                     s[4 * i + 2] = w.z * s[4 * i + 2] - au.z * dot + k.z * v_in;
                     s[4 * i + 3] = w.w * s[4 * i + 3] - au.w * dot + k.w * v_in;
-                    o += q.x * s[4 * i] + q.y * s[4 * i + 1] + q.z * s[4 * i + 2] + q.w * s[4 * i + 3];
+                    if (SEG != 1) {
+                        const float4 q = r4[i];
+                        o0 += q.x * s[4 * i]; o1 += q.y * s[4 * i + 1]; o2 += q.z * s[4 * i + 2]; o3 += q.w * s[4 * i + 3];
+                    }
                 }
             }
-            for (int w = split >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-            if (live && part == 0) out[((size_t)(c0 + tok) * H + h) * V + col] = o;
+            if (SEG != 1) {
+                float o = (o0 + o1) + (o2 + o3);
+                for (int w = split >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+                if (live && part == 0) out[((size_t)(c0 + tok) * H + h) * V + col] = o;
+            }
         }
     }
-    if (live) {
+    if (live && SEG != 2) {
 #pragma unroll
         for (int i = 0; i < kDeltaPer; ++i) {
             const int d = part * kDeltaPer + i;
             if (d < D) srow[d] = s[i];
         }
+    }
+}
+
+// The chain over a request's segments: start(0) is the slot's state, start(s + 1) = P_s start(s) + E_s,
+// and the slot's state becomes the start after the last segment.  A block owns kChainRows value rows of
+// a head; thread d owns key channel d of each.  With the rows stored [value, key]:
+//     next[v][d] = E[v][d] + sum_c P[c][d] * cur[v][c]      (P's column c lies in row V + c of seg_acc)
+constexpr int kChainRows = 8;
+
+__global__ void __launch_bounds__(256)
+delta_chain_kernel(float* __restrict__ state, int n_slots, const float* __restrict__ seg_acc, float* __restrict__ seg_start,
+                   const int* __restrict__ q_start, const int* __restrict__ table_rows, int H, int D, int V, int seg_len,
+                   int max_segs) {
+    extern __shared__ __align__(16) float cur[];    // [D][kChainRows]
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * kChainRows, d = threadIdx.x;
+    const int L = q_start[r + 1] - q_start[r];
+    const int n_seg = (L + seg_len - 1) / seg_len;
+    const int slot = table_rows[r];
+    if (n_seg <= 0) return;
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    const int Vs = V + D;
+    const bool mine = d < D;
+    float acc[kChainRows];
+    float* srow = state + ((size_t)slot * H + h) * V * D;
+#pragma unroll
+    for (int v = 0; v < kChainRows; ++v) acc[v] = (mine && v0 + v < V) ? srow[(size_t)(v0 + v) * D + d] : 0.f;
+    for (int sg = 0; sg < n_seg; ++sg) {
+        const size_t z = (size_t)r * max_segs + sg;
+        if (mine) {
+            float* st = seg_start + (z * H + h) * V * D;
+#pragma unroll
+            for (int v = 0; v < kChainRows; ++v) {
+                if (v0 + v < V) st[(size_t)(v0 + v) * D + d] = acc[v];
+                cur[d * kChainRows + v] = acc[v];
+            }
+        }
+        __syncthreads();
+        const float* E = seg_acc + (z * H + h) * Vs * D;
+        const float* P = E + (size_t)V * D;
+        if (mine) {
+#pragma unroll
+            for (int v = 0; v < kChainRows; ++v) acc[v] = v0 + v < V ? E[(size_t)(v0 + v) * D + d] : 0.f;
+#pragma unroll 8
+            for (int c = 0; c < D; ++c) {
+                const float p = P[(size_t)c * D + d];
+                const float4 a = *reinterpret_cast<const float4*>(cur + c * kChainRows);
+                const float4 b = *reinterpret_cast<const float4*>(cur + c * kChainRows + 4);
+                acc[0] += p * a.x; acc[1] += p * a.y; acc[2] += p * a.z; acc[3] += p * a.w;
+                acc[4] += p * b.x; acc[5] += p * b.y; acc[6] += p * b.z; acc[7] += p * b.w;
+            }
+        }
+        __syncthreads();                            // every lane has read cur
+    }
+    if (mine) {
+#pragma unroll
+        for (int v = 0; v < kChainRows; ++v)
+            if (v0 + v < V) srow[(size_t)(v0 + v) * D + d] = acc[v];
     }
 }
 
@@ -375,32 +478,65 @@ LSB_API int lsb_channel_delta_prep(const void* proj, int dtype, long long ld, in
 
 // mode 0: scalar gates (vecs [T, 2, G, D]: q then k; scal [T, 2, H]: fade then beta); mode 1: channel
 // gates (vecs [T, H, 5, D]: r, k, u, a * u, w).  vals [T, H, V]; state [slots, H, V, D]; out [T, H, V].
+// seg_len > 0 with scratch given and a portion longer than a segment: portions are walked in segments
+// side by side; seg_acc [requests * max_segs, H, V + D, D] and seg_start [requests * max_segs, H, V, D]
+// with max_segs = ceil(max_q_len / seg_len).
 LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const float* vals, float* state, int n_slots,
                            const int* q_start, const int* table_rows, int n_requests, float* out, int H, int G, int D,
-                           int V, cudaStream_t stream) {
+                           int V, int seg_len, int max_q_len, float* seg_acc, float* seg_start, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || D > kDeltaPer * kDeltaMaxSplit || n_requests > 65535 || H > 65535 ||
         (mode == 0 && (G <= 0 || H % G || !scal)) || (mode != 0 && mode != 1))
         return (int)cudaErrorInvalidValue;
     int split = 1;
     while (split * kDeltaPer < D) split *= 2;
-    int threads = ((V * split + 31) / 32) * 32;
-    if (threads > kDeltaThreads) threads = kDeltaThreads;
-    const int cols = threads / split;
+    const bool segmented = seg_len > 0 && seg_acc && seg_start && max_q_len > seg_len;
+    const int max_segs = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
+    if ((long long)n_requests * max_segs > 65535) return (int)cudaErrorInvalidValue;
     const int NV = mode == 0 ? 2 : 5;
-    const size_t smem = (size_t)kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
-    dim3 grid((V + cols - 1) / cols, H, n_requests);
-    int rc = 0;
-    if (mode == 0) {
-        if (smem > 48 * 1024) rc = (int)cudaFuncSetAttribute(delta_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (rc) return rc;
-        return lsb_launch(delta_scan_kernel<0>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, n_slots,
-                          q_start, table_rows, out, H, G, D, V, split);
-    }
-    if (smem > 48 * 1024) rc = (int)cudaFuncSetAttribute(delta_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (rc) return rc;
-    return lsb_launch(delta_scan_kernel<1>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, n_slots, q_start,
-                      table_rows, out, H, H, D, V, split);
+    if (mode != 0) G = H;
+    // walked columns -> threads of a block, blocks, shared memory
+    auto shape = [&](int columns, int* threads, dim3* grid, size_t* smem) {
+        int th = ((columns * split + 31) / 32) * 32;
+        if (th > kDeltaThreads) th = kDeltaThreads;
+        const int cols = th / split;
+        *threads = th;
+        *grid = dim3((columns + cols - 1) / cols, H, n_requests * max_segs);
+        *smem = (size_t)kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
+    };
+#define LSB_DELTA_LAUNCH(MODE, SEG, COLUMNS)                                                                   \
+    do {                                                                                                       \
+        int threads; dim3 grid; size_t smem;                                                                   \
+        shape(COLUMNS, &threads, &grid, &smem);                                                                \
+        if (smem > 48 * 1024) {                                                                                \
+            int rc = (int)cudaFuncSetAttribute(delta_scan_kernel<MODE, SEG>,                                   \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            if (rc) return rc;                                                                                 \
+        }                                                                                                      \
+        int rc = lsb_launch(delta_scan_kernel<MODE, SEG>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, \
+                            n_slots, q_start, table_rows, out, H, G, D, V, split, seg_len, max_segs, seg_acc,  \
+                            (const float*)seg_start);                                                          \
+        if (rc) return rc;                                                                                     \
+    } while (0)
+#define LSB_DELTA_MODE(MODE)                                                                                   \
+    do {                                                                                                       \
+        if (!segmented) {                                                                                      \
+            LSB_DELTA_LAUNCH(MODE, 0, V);                                                                      \
+        } else {                                                                                               \
+            LSB_DELTA_LAUNCH(MODE, 1, V + D);                                                                  \
+            const int threads = ((D + 31) / 32) * 32;                                                          \
+            int rc = lsb_launch(delta_chain_kernel, dim3((V + kChainRows - 1) / kChainRows, H, n_requests),    \
+                                dim3(threads), (size_t)D * kChainRows * sizeof(float), stream, 1, state, n_slots, \
+                                (const float*)seg_acc, seg_start, q_start, table_rows, H, D, V, seg_len, max_segs); \
+            if (rc) return rc;                                                                                 \
+            LSB_DELTA_LAUNCH(MODE, 2, V);                                                                      \
+        }                                                                                                      \
+    } while (0)
+    if (mode == 0) LSB_DELTA_MODE(0);
+    else LSB_DELTA_MODE(1);
+#undef LSB_DELTA_MODE
+#undef LSB_DELTA_LAUNCH
+    return 0;
 }
 
 LSB_API int lsb_delta_output(const float* x, const float* w, int w_len, const void* gate, long long gate_stride,

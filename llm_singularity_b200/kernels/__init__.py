@@ -1332,6 +1332,9 @@ def channel_delta_prep(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, h
           _ll(remove_raw.stride(0)), _p(remove_bias), _f(decay_rate), _f(unit_eps), _p(vecs), _p(v), _stream(proj))
 
 
+DELTA_SEGMENT = 128             # tokens of a segment when long portions of a delta-rule memory are walked in segments (0: never)
+
+
 def delta_scan(form: str, vecs: torch.Tensor, scal: Optional[torch.Tensor], vals: torch.Tensor, state: torch.Tensor, ctx,
                out: torch.Tensor, heads: int, key_heads: int, key_dim: int, value_dim: int) -> None:
     """The walk of a delta-rule memory, each request from its slot's state (``state`` [slots, heads,
@@ -1356,9 +1359,18 @@ def delta_scan(form: str, vecs: torch.Tensor, scal: Optional[torch.Tensor], vals
             raise KernelError("delta_scan: scal must be [T, 2 * heads]")
     if key_dim > delta_max_key_dim():
         raise KernelError(f"delta_scan: key_dim {key_dim} is not supported (at most {delta_max_key_dim()})")
+    # a few requests with long portions: segments walked side by side (three times the arithmetic, a
+    # chain a segment long); many requests, short portions and single tokens: one walk each
+    seg, seg_acc, seg_start = 0, None, None
+    if DELTA_SEGMENT and ctx.max_q_len >= 4 * DELTA_SEGMENT and ctx.n_requests <= 8:
+        seg = DELTA_SEGMENT
+        n = ctx.n_requests * -(-ctx.max_q_len // seg)
+        seg_acc = torch.empty(n * heads * (value_dim + key_dim) * key_dim, dtype=torch.float32, device=out.device)
+        seg_start = torch.empty(n * heads * value_dim * key_dim, dtype=torch.float32, device=out.device)
     _call("delta_rule", "lsb_delta_scan", _i(0 if form == "scalar" else 1), _p(vecs), _p(scal if form == "scalar" else None),
           _p(vals), _p(state), _i(state.shape[0]), _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out),
-          _i(heads), _i(key_heads), _i(key_dim), _i(value_dim), _stream(out))
+          _i(heads), _i(key_heads), _i(key_dim), _i(value_dim), _i(seg), _i(ctx.max_q_len), _p(seg_acc), _p(seg_start),
+          _stream(out))
 
 
 _DELTA_GATES = {"none": 0, "sigmoid": 1, "silu": 2}

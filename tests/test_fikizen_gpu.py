@@ -70,6 +70,34 @@ def test_portions_of_any_size(tmp_path, dtype, name, n=150):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mix_a", "mix_c"])
+def test_long_portions_walked_in_segments(tmp_path, dtype, name, monkeypatch, n=150):
+    """The memories' long portions cut into segments of 16 and of 5 tokens that are walked side by side:
+    a whole prompt, a long portion after a short one, and two long portions of unequal length in one
+    batch, against the plain model."""
+    from llm_singularity_b200 import kernels as K
+    from llm_singularity_b200.engine.batch import StepEntry
+    cfg = U.CONFIGS[name]
+    W, path = _setup(tmp_path, cfg, 11, rank=U.DECAY_RANKS[name])
+    toks, other = U.tokens_for(cfg, n, 4), U.tokens_for(cfg, 97, 5)
+    want, want_other = U.plain_logits(cfg, W, toks), U.plain_logits(cfg, W, other)
+    for seg in (16, 5):
+        monkeypatch.setattr(K, "DELTA_SEGMENT", seg)
+        r = U.make_runner(path, dtype, pages=24)                  # (a runner keeps the graphs of the shapes it has met)
+        for cuts in ([n], [3, n - 4, 1], [70, 80], [n]):
+            got = U.run_cuts(r, "p", toks, cuts)
+            assert U.close(got, want, dtype), (seg, cuts, U.rel_err(got, want))
+        assert r.open("x") and r.open("y")
+        a = r.step([StepEntry("x", toks[:90], list(range(90))), StepEntry("y", other[:96], list(range(96)))]).float().cpu()
+        b = r.step([StepEntry("y", other[96:], [0]), StepEntry("x", toks[90:], list(range(n - 90)))]).float().cpu()
+        r.close("x"); r.close("y")
+        r.check_kernels()
+        assert U.close(torch.cat([a[:90], b[1:]]), want, dtype), seg
+        assert U.close(torch.cat([a[90:], b[:1]]), want_other, dtype), seg
+        r.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mix_a", "mix_b", "mix_c"])
 def test_mixed_batches_with_slots_and_pages_used_again(tmp_path, dtype, name):
     """Four requests of unequal length stepped together (portions beside single tokens, a request
@@ -366,11 +394,16 @@ def _rand(*shape, g, scale=1.0):
 
 @pytest.mark.parametrize("H, G, D, V", [(3, 3, 16, 16), (4, 2, 32, 24), (2, 1, 64, 128), (5, 5, 6, 10), (6, 1, 48, 7),
                                         (1, 1, 128, 64), (2, 2, 200, 33), (8, 4, 96, 96)])
-def test_delta_walk_with_state_carried_and_slots_used_again(H, G, D, V):
+@pytest.mark.parametrize("segment", [None, 16, 7])
+def test_delta_walk_with_state_carried_and_slots_used_again(H, G, D, V, segment, monkeypatch):
     """Both forms of the walk: four requests in changing portions (single tokens beside portions of
     hundreds), their slots in another order than the batch's, a slot given to a new request after it
-    was zeroed, against a float64 walk of each request alone."""
+    was zeroed, against a float64 walk of each request alone.  With short segments the long portions
+    are walked in segments side by side (whole ones and a ragged last one, beside requests of one
+    token in the same launch), the short steps in one walk each."""
     from llm_singularity_b200 import kernels as K
+    if segment is not None:
+        monkeypatch.setattr(K, "DELTA_SEGMENT", segment)
     g = torch.Generator().manual_seed(D + V)
     lens = {"a": 260, "b": 40, "c": 9, "d": 25}
     slot = {"a": 2, "b": 0, "c": 3, "d": 3}                       # d takes c's slot once c has ended
@@ -428,11 +461,15 @@ def test_delta_walk_with_state_carried_and_slots_used_again(H, G, D, V):
     K.check_status()
 
 
-def test_delta_walk_reads_a_write_from_far_back():
+@pytest.mark.parametrize("segment", [None, 16])
+def test_delta_walk_reads_a_write_from_far_back(segment, monkeypatch):
     """Scalar form, no fading: token 2 writes value x under key e0 with full strength, every later
     token writes under other keys, and the query at the very end, 400 tokens and many steps later,
-    asks along e0: the answer is x exactly.  With a fade of 0.99 a token it is x * 0.99^(n-3)."""
+    asks along e0: the answer is x exactly.  With a fade of 0.99 a token it is x * 0.99^(n-3).  With
+    segments the write has to pass through a dozen segments' products."""
     from llm_singularity_b200 import kernels as K
+    if segment is not None:
+        monkeypatch.setattr(K, "DELTA_SEGMENT", segment)
     H, D, V, n = 2, 32, 16, 403
     g = torch.Generator().manual_seed(5)
     x = torch.randn(H, V, generator=g)
