@@ -27,7 +27,7 @@
 // The walk: a block owns (request, head, a tile of value columns) and takes the request's tokens in
 // order, so the result does not depend on how a prompt was cut.  A column's key channels are dealt to
 // `split` neighbouring lanes, 32 each, kept in registers; dots are finished by shuffles.  The tokens'
-// vectors come through shared memory in chunks of 16 tokens.
+// vectors come through shared memory in chunks of 16 tokens, a chunk copied while the one before is walked.
 //
 // Long portions are cut into segments that are walked side by side, since a walk is a chain of
 // dependent steps and one portion alone gives the chip few of them.  A token's step is linear in the
@@ -37,6 +37,7 @@
 // start(s + 1) = P_s start(s) + E_s; every segment is then walked again from its start for the outputs.
 // The sums form in another order than in one walk: equal beyond rounding.
 #include "common.cuh"
+#include <type_traits>
 
 LSB_DEFINE_STATUS()
 
@@ -47,6 +48,14 @@ constexpr int kDeltaPad = 4;         // words between the shares of neighbouring
 constexpr int kDeltaMaxSplit = 8;
 
 __device__ __forceinline__ float delta_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ void delta_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void delta_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void delta_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void delta_copy_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 __device__ __forceinline__ float delta_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // ------------------------------------------------------------------ scalar gates: preparation
@@ -195,12 +204,14 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     extern __shared__ __align__(16) float sh[];
     const int cols = blockDim.x / split;
     const int Dp = split * (kDeltaPer + kDeltaPad);
-    float* vec_sh = sh;                             // [chunk][NV][Dp]
-    float* val_sh = vec_sh + kDeltaChunk * NV * Dp; // [chunk][cols]
-    float* scal_sh = val_sh + kDeltaChunk * cols;   // [chunk][2]
+    float* vec_sh = sh;                                 // [2][chunk][NV][Dp]
+    float* val_sh = vec_sh + 2 * kDeltaChunk * NV * Dp; // [2][chunk][cols]
+    float* scal_sh = val_sh + 2 * kDeltaChunk * cols;   // [2][chunk][2]
+    const bool wide = (D & 3) == 0 && (reinterpret_cast<size_t>(vecs) & 15) == 0;
     lsb_pdl_launch_dependents();
-    // (channels past D are never staged: zero once, so that a lane's unused registers stay zero)
-    for (int idx = threadIdx.x; idx < kDeltaChunk * NV * Dp; idx += blockDim.x) vec_sh[idx] = 0.f;
+    // (channels past D and value columns past V are never staged: zero once, so that a lane's unused
+    // registers stay zero and the identity's columns meet no write)
+    for (int idx = threadIdx.x; idx < 2 * kDeltaChunk * (NV * Dp + cols); idx += blockDim.x) vec_sh[idx] = 0.f;
     lsb_pdl_wait();
     const int r = SEG ? blockIdx.z / max_segs : blockIdx.z, sidx = SEG ? blockIdx.z % max_segs : 0;
     const int h = blockIdx.y;
@@ -231,32 +242,58 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
         else s[i] = (live && d < D) ? first[d] : 0.f;
     }
     const int g = MODE == 0 ? h / (H / G) : 0;
-    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk) {
+    // A chunk's operands arrive by asynchronous copies into one of two buffers while the chunk before is
+    // walked: 16 bytes a copy where the key size and the addresses allow, 4 bytes otherwise.
+    auto stage = [&](int b, int c0) {
         const int n = min(kDeltaChunk, t1 - c0);
-        __syncthreads();                            // the chunk before has been walked by every lane
-        for (int idx = threadIdx.x; idx < n * NV * D; idx += blockDim.x) {
-            const int tok = idx / (NV * D), rem = idx - tok * NV * D, v = rem / D, d = rem - v * D;
-            const size_t src = MODE == 0 ? ((size_t)(c0 + tok) * 2 + v) * G * D + (size_t)g * D + d
-                                         : (((size_t)(c0 + tok) * H + h) * NV + v) * D + d;
-            vec_sh[(tok * NV + v) * Dp + (d / kDeltaPer) * (kDeltaPer + kDeltaPad) + d % kDeltaPer] = vecs[src];
+        float* vdst = vec_sh + b * (kDeltaChunk * NV * Dp);
+        if (wide) {
+            const int D4 = D >> 2;
+            for (int idx = threadIdx.x; idx < n * NV * D4; idx += blockDim.x) {
+                const int tok = idx / (NV * D4), rem = idx - tok * NV * D4, v = rem / D4, d = (rem - v * D4) << 2;
+                const size_t src = MODE == 0 ? ((size_t)(c0 + tok) * 2 + v) * G * D + (size_t)g * D + d
+                                             : (((size_t)(c0 + tok) * H + h) * NV + v) * D + d;
+                delta_copy16(vdst + (tok * NV + v) * Dp + (d / kDeltaPer) * (kDeltaPer + kDeltaPad) + d % kDeltaPer, vecs + src);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < n * NV * D; idx += blockDim.x) {
+                const int tok = idx / (NV * D), rem = idx - tok * NV * D, v = rem / D, d = rem - v * D;
+                const size_t src = MODE == 0 ? ((size_t)(c0 + tok) * 2 + v) * G * D + (size_t)g * D + d
+                                             : (((size_t)(c0 + tok) * H + h) * NV + v) * D + d;
+                delta_copy4(vdst + (tok * NV + v) * Dp + (d / kDeltaPer) * (kDeltaPer + kDeltaPad) + d % kDeltaPer, vecs + src);
+            }
         }
+        float* wdst = val_sh + b * (kDeltaChunk * cols);
         for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
             const int tok = idx / cols, c = idx - tok * cols;
-            val_sh[idx] = col0 + c < V ? vals[((size_t)(c0 + tok) * H + h) * V + col0 + c] : 0.f;
+            if (col0 + c < V) delta_copy4(wdst + idx, vals + ((size_t)(c0 + tok) * H + h) * V + col0 + c);
         }
         if (MODE == 0) {
             for (int idx = threadIdx.x; idx < n * 2; idx += blockDim.x)
-                scal_sh[idx] = scal[(size_t)(c0 + idx / 2) * 2 * H + (size_t)(idx & 1) * H + h];
+                delta_copy4(scal_sh + b * (kDeltaChunk * 2) + idx, scal + (size_t)(c0 + idx / 2) * 2 * H + (size_t)(idx & 1) * H + h);
         }
+    };
+    __syncthreads();                                // the zeros are in place before a copy lands among them
+    if (t0 < t1) stage(0, t0);
+    delta_copy_commit();
+    int buf = 0;
+    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk, buf ^= 1) {
+        const int n = min(kDeltaChunk, t1 - c0);
+        if (c0 + kDeltaChunk < t1) stage(buf ^ 1, c0 + kDeltaChunk);
+        delta_copy_commit();
+        delta_copy_wait_but_one();                  // this chunk's copies have landed; the next one's may fly
         __syncthreads();
+        const float* vec_b = vec_sh + buf * (kDeltaChunk * NV * Dp);
+        const float* val_b = val_sh + buf * (kDeltaChunk * cols);
+        const float* scal_b = scal_sh + buf * (kDeltaChunk * 2);
         for (int tok = 0; tok < n; ++tok) {
-            const float* vb = vec_sh + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
-            const float v_in = val_sh[tok * cols + lc];
+            const float* vb = vec_b + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
+            const float v_in = val_b[tok * cols + lc];
             // (dots gather in four partial sums, so that a token's chain of dependent additions is a
             // quarter as long; every walk sums in this same order)
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
             if (MODE == 0) {
-                const float fade = scal_sh[tok * 2], beta = scal_sh[tok * 2 + 1];
+                const float fade = scal_b[tok * 2], beta = scal_b[tok * 2 + 1];
                 const float4* q4 = reinterpret_cast<const float4*>(vb);
                 const float4* k4 = reinterpret_cast<const float4*>(vb + Dp);
                 float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
@@ -311,6 +348,7 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
                 if (live && part == 0) out[((size_t)(c0 + tok) * H + h) * V + col] = o;
             }
         }
+        __syncthreads();                            // every lane has walked this buffer before it is filled again
     }
     if (live && SEG != 2) {
 #pragma unroll
@@ -323,63 +361,96 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
 
 // The chain over a request's segments: start(0) is the slot's state, start(s + 1) = P_s start(s) + E_s,
 // and the slot's state becomes the start after the last segment.  A block owns kChainRows value rows of
-// a head; thread d owns key channel d of each.  With the rows stored [value, key]:
+// a head.  With the rows stored [value, key]:
 //     next[v][d] = E[v][d] + sum_c P[c][d] * cur[v][c]      (P's column c lies in row V + c of seg_acc)
+// Thread (d, part) sums a share of the c (a quarter; a half for key sizes above 128) for all the block's
+// rows at key channel d; the shares meet in shared memory, always in the same order, and the thread then
+// keeps its part of the rows.
 constexpr int kChainRows = 8;
+constexpr int kChainBatch = 16;
 
-__global__ void __launch_bounds__(256)
+template <int kChainSplit>
+__global__ void __launch_bounds__(512)
 delta_chain_kernel(float* __restrict__ state, int n_slots, const float* __restrict__ seg_acc, float* __restrict__ seg_start,
                    const int* __restrict__ q_start, const int* __restrict__ table_rows, int H, int D, int V, int seg_len,
                    int max_segs) {
-    extern __shared__ __align__(16) float cur[];    // [D][kChainRows]
+    constexpr int kChainOwn = kChainRows / kChainSplit;
+    extern __shared__ __align__(16) float chain_sh[];
+    const int Dr = blockDim.x;                       // D rounded up to whole warps
+    const int cper = ((D + kChainSplit * kChainBatch - 1) / (kChainSplit * kChainBatch)) * kChainBatch;
+    float* cur = chain_sh;                           // [kChainSplit * cper][kChainRows], zeros past D
+    float* part = cur + kChainSplit * cper * kChainRows;   // [kChainSplit][kChainRows][Dr]
     lsb_pdl_launch_dependents();
+    for (int i = threadIdx.y * Dr + threadIdx.x; i < kChainSplit * cper * kChainRows; i += Dr * kChainSplit) cur[i] = 0.f;
     lsb_pdl_wait();
-    const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * kChainRows, d = threadIdx.x;
+    const int r = blockIdx.z, h = blockIdx.y, v0 = blockIdx.x * kChainRows, d = threadIdx.x, pt = threadIdx.y;
     const int L = q_start[r + 1] - q_start[r];
     const int n_seg = (L + seg_len - 1) / seg_len;
     const int slot = table_rows[r];
     if (n_seg <= 0) return;
     if (slot < 0 || slot >= n_slots) {
-        if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+        if (threadIdx.x == 0 && threadIdx.y == 0) lsb_set_status(LSB_BAD_ROW);
         return;
     }
     const int Vs = V + D;
     const bool mine = d < D;
-    float acc[kChainRows];
+    const int dd = mine ? d : 0;
+    const int my0 = v0 + pt * kChainOwn;             // the first of the rows this thread keeps
+    float own[kChainOwn];
     float* srow = state + ((size_t)slot * H + h) * V * D;
 #pragma unroll
-    for (int v = 0; v < kChainRows; ++v) acc[v] = (mine && v0 + v < V) ? srow[(size_t)(v0 + v) * D + d] : 0.f;
+    for (int j = 0; j < kChainOwn; ++j) own[j] = (mine && my0 + j < V) ? srow[(size_t)(my0 + j) * D + d] : 0.f;
+    __syncthreads();                                 // the zeros are in place
     for (int sg = 0; sg < n_seg; ++sg) {
         const size_t z = (size_t)r * max_segs + sg;
+        const float* E = seg_acc + (z * H + h) * Vs * D;
+        const float* P = E + (size_t)V * D;
+        float e[kChainOwn];
         if (mine) {
             float* st = seg_start + (z * H + h) * V * D;
 #pragma unroll
-            for (int v = 0; v < kChainRows; ++v) {
-                if (v0 + v < V) st[(size_t)(v0 + v) * D + d] = acc[v];
-                cur[d * kChainRows + v] = acc[v];
+            for (int j = 0; j < kChainOwn; ++j) {
+                if (my0 + j < V) st[(size_t)(my0 + j) * D + d] = own[j];
+                cur[d * kChainRows + pt * kChainOwn + j] = own[j];
+                e[j] = my0 + j < V ? E[(size_t)(my0 + j) * D + d] : 0.f;
             }
         }
         __syncthreads();
-        const float* E = seg_acc + (z * H + h) * Vs * D;
-        const float* P = E + (size_t)V * D;
-        if (mine) {
+        float acc[kChainRows];
 #pragma unroll
-            for (int v = 0; v < kChainRows; ++v) acc[v] = v0 + v < V ? E[(size_t)(v0 + v) * D + d] : 0.f;
-#pragma unroll 8
-            for (int c = 0; c < D; ++c) {
-                const float p = P[(size_t)c * D + d];
-                const float4 a = *reinterpret_cast<const float4*>(cur + c * kChainRows);
-                const float4 b = *reinterpret_cast<const float4*>(cur + c * kChainRows + 4);
-                acc[0] += p * a.x; acc[1] += p * a.y; acc[2] += p * a.z; acc[3] += p * a.w;
-                acc[4] += p * b.x; acc[5] += p * b.y; acc[6] += p * b.z; acc[7] += p * b.w;
+        for (int v = 0; v < kChainRows; ++v) acc[v] = 0.f;
+        // (a batch of P's rows is asked for at once, so that their latencies overlap; rows past D meet
+        // the zeros of cur)
+        for (int c0 = pt * cper; c0 < (pt + 1) * cper; c0 += kChainBatch) {
+            float p[kChainBatch];
+#pragma unroll
+            for (int j = 0; j < kChainBatch; ++j) p[j] = P[(size_t)min(c0 + j, D - 1) * D + dd];
+#pragma unroll
+            for (int j = 0; j < kChainBatch; ++j) {
+                const float4 a = *reinterpret_cast<const float4*>(cur + (c0 + j) * kChainRows);
+                const float4 b = *reinterpret_cast<const float4*>(cur + (c0 + j) * kChainRows + 4);
+                acc[0] += p[j] * a.x; acc[1] += p[j] * a.y; acc[2] += p[j] * a.z; acc[3] += p[j] * a.w;
+                acc[4] += p[j] * b.x; acc[5] += p[j] * b.y; acc[6] += p[j] * b.z; acc[7] += p[j] * b.w;
             }
         }
-        __syncthreads();                            // every lane has read cur
+#pragma unroll
+        for (int v = 0; v < kChainRows; ++v) part[(pt * kChainRows + v) * Dr + d] = acc[v];
+        __syncthreads();                             // every lane has read cur; the quarters are in place
+        if (mine) {
+#pragma unroll
+            for (int j = 0; j < kChainOwn; ++j) {
+                float sum = e[j];
+#pragma unroll
+                for (int g = 0; g < kChainSplit; ++g) sum += part[(g * kChainRows + pt * kChainOwn + j) * Dr + d];
+                own[j] = sum;
+            }
+        }
+        // (the quarters are written again only after the next segment's first barrier)
     }
     if (mine) {
 #pragma unroll
-        for (int v = 0; v < kChainRows; ++v)
-            if (v0 + v < V) srow[(size_t)(v0 + v) * D + d] = acc[v];
+        for (int j = 0; j < kChainOwn; ++j)
+            if (my0 + j < V) srow[(size_t)(my0 + j) * D + d] = own[j];
     }
 }
 
@@ -502,7 +573,16 @@ LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const
         const int cols = th / split;
         *threads = th;
         *grid = dim3((columns + cols - 1) / cols, H, n_requests * max_segs);
-        *smem = (size_t)kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
+        *smem = (size_t)2 * kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
+    };
+    const int Dr = ((D + 31) / 32) * 32;
+    auto chain = [&](auto split_c) -> int {
+        constexpr int SPLIT = decltype(split_c)::value;
+        const int cper = ((D + SPLIT * kChainBatch - 1) / (SPLIT * kChainBatch)) * kChainBatch;
+        const size_t csm = (size_t)SPLIT * kChainRows * (cper + Dr) * sizeof(float);
+        return lsb_launch(delta_chain_kernel<SPLIT>, dim3((V + kChainRows - 1) / kChainRows, H, n_requests), dim3(Dr, SPLIT),
+                          csm, stream, 1, state, n_slots, (const float*)seg_acc, seg_start, q_start, table_rows, H, D, V,
+                          seg_len, max_segs);
     };
 #define LSB_DELTA_LAUNCH(MODE, SEG, COLUMNS)                                                                   \
     do {                                                                                                       \
@@ -524,10 +604,7 @@ LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const
             LSB_DELTA_LAUNCH(MODE, 0, V);                                                                      \
         } else {                                                                                               \
             LSB_DELTA_LAUNCH(MODE, 1, V + D);                                                                  \
-            const int threads = ((D + 31) / 32) * 32;                                                          \
-            int rc = lsb_launch(delta_chain_kernel, dim3((V + kChainRows - 1) / kChainRows, H, n_requests),    \
-                                dim3(threads), (size_t)D * kChainRows * sizeof(float), stream, 1, state, n_slots, \
-                                (const float*)seg_acc, seg_start, q_start, table_rows, H, D, V, seg_len, max_segs); \
+            int rc = Dr <= 128 ? chain(std::integral_constant<int, 4>()) : chain(std::integral_constant<int, 2>()); \
             if (rc) return rc;                                                                                 \
             LSB_DELTA_LAUNCH(MODE, 2, V);                                                                      \
         }                                                                                                      \
