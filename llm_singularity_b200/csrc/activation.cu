@@ -56,21 +56,34 @@ LSB_API int lsb_gated_act(const void* gate_up, void* out, int dtype, int tokens,
 // (c_pos = softplus(p), c_neg = 1/2 + softplus(q) for the stored p and q).
 enum : int { LSB_ACT_BENT_SQUARE = 4 };
 
+__device__ __forceinline__ float plain_act_of(float z, int act, float c_pos, float c_neg) {
+    if (act == LSB_ACT_SILU) return z / (1.f + expf(-z));
+    if (act == LSB_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608f * (z + 0.044715f * z * z * z)));
+    if (act == LSB_ACT_BENT_SQUARE) return z > 0.f ? c_pos * z * z + 0.5f * z : c_neg * (expm1f(z) - z) + 0.5f * z;
+    return z;
+}
+
+// 16 bytes a thread and turn where the count and both addresses allow (`wide`), one value otherwise.
 template <typename T>
-__global__ void plain_act_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int act, float c_pos, float c_neg) {
+__global__ void plain_act_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int act, float c_pos,
+                                 float c_neg, int wide) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
+    constexpr int N = 16 / (int)sizeof(T);
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; idx < total; idx += stride) {
-        const float z = lsb_to_float(x[idx]);
-        float a;
-        if (act == LSB_ACT_SILU) a = z / (1.f + expf(-z));
-        else if (act == LSB_ACT_GELU_TANH) a = 0.5f * z * (1.f + tanhf(0.7978845608f * (z + 0.044715f * z * z * z)));
-        else if (act == LSB_ACT_BENT_SQUARE) a = z > 0.f ? c_pos * z * z + 0.5f * z : c_neg * (expm1f(z) - z) + 0.5f * z;
-        else a = z;
-        out[idx] = lsb_from_float<T>(a);
+    if (wide) {
+        const long long groups = total / N;
+        for (; idx < groups; idx += stride) {
+            uint4 raw = reinterpret_cast<const uint4*>(x)[idx];
+            T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = lsb_from_float<T>(plain_act_of(lsb_to_float(v[i]), act, c_pos, c_neg));
+            reinterpret_cast<uint4*>(out)[idx] = raw;
+        }
+        return;
     }
+    for (; idx < total; idx += stride) out[idx] = lsb_from_float<T>(plain_act_of(lsb_to_float(x[idx]), act, c_pos, c_neg));
 }
 
 LSB_API int lsb_plain_act(const void* x, void* out, int dtype, long long total, int act, float c_pos, float c_neg,
@@ -78,10 +91,14 @@ LSB_API int lsb_plain_act(const void* x, void* out, int dtype, long long total, 
     if (total <= 0) return 0;
     if (act < LSB_ACT_SILU || act > LSB_ACT_BENT_SQUARE) return (int)cudaErrorInvalidValue;
     const int threads = 256;
-    long long blocks = (total + threads - 1) / threads;
+    const int per = dtype == LSB_F32 ? 4 : 8;    // values in 16 bytes
+    const int wide = total % 8 == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(out)) & 15) == 0;
+    const long long work = wide ? total / per : total;
+    long long blocks = (work + threads - 1) / threads;
+    if (blocks < 1) blocks = 1;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(plain_act_kernel<T>, dim3((int)blocks), dim3(threads), 0, stream, 1,
-                                                (const T*)x, (T*)out, total, act, c_pos, c_neg));
+                                                (const T*)x, (T*)out, total, act, c_pos, c_neg, wide));
     return 0;
 }
 

@@ -234,12 +234,17 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     float* srow = SEG == 1 ? seg_acc + (((size_t)blockIdx.z * H + h) * Vs + (live ? col : 0)) * D
                            : state + (((size_t)slot * H + h) * V + (live ? col : 0)) * D;
     const float* first = SEG == 2 ? seg_start + (((size_t)blockIdx.z * H + h) * V + (live ? col : 0)) * D : srow;
-    float s[kDeltaPer];
+    // (the state's share lives in pairs: the walk's arithmetic is the two-wide 32-bit FMA of sm_100,
+    // one instruction for two channels, each channel rounded as the one-wide form rounds it)
+    float2 s[kDeltaPer / 2];
 #pragma unroll
     for (int i = 0; i < kDeltaPer; ++i) {
         const int d = part * kDeltaPer + i;
-        if (SEG == 1) s[i] = (live && col >= V && d == col - V) ? 1.f : 0.f;
-        else s[i] = (live && d < D) ? first[d] : 0.f;
+        float x;
+        if (SEG == 1) x = (live && col >= V && d == col - V) ? 1.f : 0.f;
+        else x = (live && d < D) ? first[d] : 0.f;
+        if (i & 1) s[i >> 1].y = x;
+        else s[i >> 1].x = x;
     }
     const int g = MODE == 0 ? h / (H / G) : 0;
     // A chunk's operands arrive by asynchronous copies into one of two buffers while the chunk before is
@@ -286,33 +291,40 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
         const float* vec_b = vec_sh + buf * (kDeltaChunk * NV * Dp);
         const float* val_b = val_sh + buf * (kDeltaChunk * cols);
         const float* scal_b = scal_sh + buf * (kDeltaChunk * 2);
+#pragma unroll 2
         for (int tok = 0; tok < n; ++tok) {
             const float* vb = vec_b + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
             const float v_in = val_b[tok * cols + lc];
             // (dots gather in four partial sums, so that a token's chain of dependent additions is a
             // quarter as long; every walk sums in this same order)
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            float2 o01 = make_float2(0.f, 0.f), o23 = make_float2(0.f, 0.f);
+            float2 d01 = make_float2(0.f, 0.f), d23 = make_float2(0.f, 0.f);
             if (MODE == 0) {
                 const float fade = scal_b[tok * 2], beta = scal_b[tok * 2 + 1];
+                const float2 fade2 = make_float2(fade, fade);
                 const float4* q4 = reinterpret_cast<const float4*>(vb);
                 const float4* k4 = reinterpret_cast<const float4*>(vb + Dp);
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 k = k4[i];
-                    s[4 * i] *= fade; s[4 * i + 1] *= fade; s[4 * i + 2] *= fade; s[4 * i + 3] *= fade;
-                    d0 += k.x * s[4 * i]; d1 += k.y * s[4 * i + 1]; d2 += k.z * s[4 * i + 2]; d3 += k.w * s[4 * i + 3];
+                    s[2 * i] = __fmul2_rn(s[2 * i], fade2);
+                    s[2 * i + 1] = __fmul2_rn(s[2 * i + 1], fade2);
+                    d01 = __ffma2_rn(make_float2(k.x, k.y), s[2 * i], d01);
+                    d23 = __ffma2_rn(make_float2(k.z, k.w), s[2 * i + 1], d23);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
+                float dot = (d01.x + d01.y) + (d23.x + d23.y);
                 for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
                 const float e = beta * (v_in - dot);
+                const float2 e2 = make_float2(e, e);
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 k = k4[i];
-                    s[4 * i] += k.x * e; s[4 * i + 1] += k.y * e; s[4 * i + 2] += k.z * e; s[4 * i + 3] += k.w * e;
+                    s[2 * i] = __ffma2_rn(make_float2(k.x, k.y), e2, s[2 * i]);
+                    s[2 * i + 1] = __ffma2_rn(make_float2(k.z, k.w), e2, s[2 * i + 1]);
                     if (SEG != 1) {
                         const float4 q = q4[i];
-                        o0 += q.x * s[4 * i]; o1 += q.y * s[4 * i + 1]; o2 += q.z * s[4 * i + 2]; o3 += q.w * s[4 * i + 3];
+                        o01 = __ffma2_rn(make_float2(q.x, q.y), s[2 * i], o01);
+                        o23 = __ffma2_rn(make_float2(q.z, q.w), s[2 * i + 1], o23);
                     }
                 }
             } else {
@@ -321,29 +333,34 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
                 const float4* u4 = reinterpret_cast<const float4*>(vb + 2 * Dp);
                 const float4* a4 = reinterpret_cast<const float4*>(vb + 3 * Dp);
                 const float4* w4 = reinterpret_cast<const float4*>(vb + 4 * Dp);
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 u = u4[i];
-                    d0 += u.x * s[4 * i]; d1 += u.y * s[4 * i + 1]; d2 += u.z * s[4 * i + 2]; d3 += u.w * s[4 * i + 3];
+                    d01 = __ffma2_rn(make_float2(u.x, u.y), s[2 * i], d01);
+                    d23 = __ffma2_rn(make_float2(u.z, u.w), s[2 * i + 1], d23);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
+                float dot = (d01.x + d01.y) + (d23.x + d23.y);
                 for (int w = split >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+                const float2 nd2 = make_float2(-dot, -dot), v2 = make_float2(v_in, v_in);
 #pragma unroll
                 for (int i = 0; i < kDeltaPer / 4; ++i) {
                     const float4 k = k4[i], au = a4[i], w = w4[i];
-                    s[4 * i] = w.x * s[4 * i] - au.x * dot + k.x * v_in;
-                    s[4 * i + 1] = w.y * s[4 * i + 1] - au.y * dot + k.y * v_in;
-                    s[4 * i + 2] = w.z * s[4 * i + 2] - au.z * dot + k.z * v_in;
-                    s[4 * i + 3] = w.w * s[4 * i + 3] - au.w * dot + k.w * v_in;
+                    // w s - (a u) dot + k v, as a product and two FMAs
+                    float2 lo = __fmul2_rn(make_float2(w.x, w.y), s[2 * i]);
+                    float2 hi = __fmul2_rn(make_float2(w.z, w.w), s[2 * i + 1]);
+                    lo = __ffma2_rn(make_float2(au.x, au.y), nd2, lo);
+                    hi = __ffma2_rn(make_float2(au.z, au.w), nd2, hi);
+                    s[2 * i] = __ffma2_rn(make_float2(k.x, k.y), v2, lo);
+                    s[2 * i + 1] = __ffma2_rn(make_float2(k.z, k.w), v2, hi);
                     if (SEG != 1) {
                         const float4 q = r4[i];
-                        o0 += q.x * s[4 * i]; o1 += q.y * s[4 * i + 1]; o2 += q.z * s[4 * i + 2]; o3 += q.w * s[4 * i + 3];
+                        o01 = __ffma2_rn(make_float2(q.x, q.y), s[2 * i], o01);
+                        o23 = __ffma2_rn(make_float2(q.z, q.w), s[2 * i + 1], o23);
                     }
                 }
             }
             if (SEG != 1) {
-                float o = (o0 + o1) + (o2 + o3);
+                float o = (o01.x + o01.y) + (o23.x + o23.y);
                 for (int w = split >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
                 if (live && part == 0) out[((size_t)(c0 + tok) * H + h) * V + col] = o;
             }
@@ -354,7 +371,7 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
 #pragma unroll
         for (int i = 0; i < kDeltaPer; ++i) {
             const int d = part * kDeltaPer + i;
-            if (d < D) srow[d] = s[i];
+            if (d < D) srow[d] = (i & 1) ? s[i >> 1].y : s[i >> 1].x;
         }
     }
 }
