@@ -71,8 +71,10 @@ struct GatedPrepArgs {
     float unit_eps;
 };
 
+constexpr int kPrepMaxThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(kDeltaThreads) gated_delta_prep_kernel(GatedPrepArgs a) {
+__global__ void __launch_bounds__(kPrepMaxThreads) gated_delta_prep_kernel(GatedPrepArgs a) {
     extern __shared__ float ch_sh[];                // the token's channels after convolution and silu
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(kDeltaThreads) gated_delta_prep_kernel(GatedPr
         ch_sh[c] = acc * delta_sigmoid(acc);
     }
     __syncthreads();
-    for (int head = warp; head < 2 * a.G; head += kDeltaThreads / 32) {
+    for (int head = warp; head < 2 * a.G; head += blockDim.x >> 5) {
         const float* hs = ch_sh + (size_t)head * a.D;
         float ss = 0.f;
         for (int d = lane; d < a.D; d += 32) ss += hs[d] * hs[d];
@@ -537,7 +539,10 @@ LSB_API int lsb_gated_delta_prep(const void* proj, int dtype, long long ld, int 
             int rc = (int)cudaFuncSetAttribute(gated_delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (rc) return rc;
         }
-        int rc = lsb_launch(gated_delta_prep_kernel<T>, dim3(tokens), dim3(kDeltaThreads), smem, stream, 1, a);
+        // (a thread for every four channels, within 128 .. 512)
+        int threads = ((C / 4 + 31) / 32) * 32;
+        threads = threads < kDeltaThreads ? kDeltaThreads : threads > kPrepMaxThreads ? kPrepMaxThreads : threads;
+        int rc = lsb_launch(gated_delta_prep_kernel<T>, dim3(tokens), dim3(threads), smem, stream, 1, a);
         if (rc || taps == 1) return rc;
         const int bx = (C + kDeltaThreads - 1) / kDeltaThreads;
         return lsb_launch(conv_state_update_kernel<T>, dim3(bx > 64 ? 64 : bx, n_requests), dim3(kDeltaThreads), 0, stream, 1,
