@@ -42,7 +42,7 @@
 LSB_DEFINE_STATUS()
 
 constexpr int kDeltaThreads = 128;
-constexpr int kDeltaChunk = 16;      // tokens staged at a time
+constexpr int kDeltaChunk = 16;      // tokens staged at a time (8 where two buffers of 16 would leave an SM fewer than four blocks)
 constexpr int kDeltaPer = 32;        // key channels of a column that one lane keeps
 constexpr int kDeltaPad = 4;         // words between the shares of neighbouring lanes in shared memory
 constexpr int kDeltaMaxSplit = 8;
@@ -201,19 +201,20 @@ __global__ void __launch_bounds__(kDeltaThreads)
 delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal, const float* __restrict__ vals,
                   float* __restrict__ state, int n_slots, const int* __restrict__ q_start,
                   const int* __restrict__ table_rows, float* __restrict__ out, int H, int G, int D, int V, int split,
-                  int seg_len, int max_segs, float* __restrict__ seg_acc, const float* __restrict__ seg_start) {
+                  int seg_len, int max_segs, float* __restrict__ seg_acc, const float* __restrict__ seg_start,
+                  int chunk) {
     constexpr int NV = MODE == 0 ? 2 : 5;          // vectors of key size a token brings
     extern __shared__ __align__(16) float sh[];
     const int cols = blockDim.x / split;
     const int Dp = split * (kDeltaPer + kDeltaPad);
     float* vec_sh = sh;                                 // [2][chunk][NV][Dp]
-    float* val_sh = vec_sh + 2 * kDeltaChunk * NV * Dp; // [2][chunk][cols]
-    float* scal_sh = val_sh + 2 * kDeltaChunk * cols;   // [2][chunk][2]
+    float* val_sh = vec_sh + 2 * chunk * NV * Dp;       // [2][chunk][cols]
+    float* scal_sh = val_sh + 2 * chunk * cols;         // [2][chunk][2]
     const bool wide = (D & 3) == 0 && (reinterpret_cast<size_t>(vecs) & 15) == 0;
     lsb_pdl_launch_dependents();
     // (channels past D and value columns past V are never staged: zero once, so that a lane's unused
     // registers stay zero and the identity's columns meet no write)
-    for (int idx = threadIdx.x; idx < 2 * kDeltaChunk * (NV * Dp + cols); idx += blockDim.x) vec_sh[idx] = 0.f;
+    for (int idx = threadIdx.x; idx < 2 * chunk * (NV * Dp + cols); idx += blockDim.x) vec_sh[idx] = 0.f;
     lsb_pdl_wait();
     const int r = SEG ? blockIdx.z / max_segs : blockIdx.z, sidx = SEG ? blockIdx.z % max_segs : 0;
     const int h = blockIdx.y;
@@ -252,8 +253,8 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     // A chunk's operands arrive by asynchronous copies into one of two buffers while the chunk before is
     // walked: 16 bytes a copy where the key size and the addresses allow, 4 bytes otherwise.
     auto stage = [&](int b, int c0) {
-        const int n = min(kDeltaChunk, t1 - c0);
-        float* vdst = vec_sh + b * (kDeltaChunk * NV * Dp);
+        const int n = min(chunk, t1 - c0);
+        float* vdst = vec_sh + b * (chunk * NV * Dp);
         if (wide) {
             const int D4 = D >> 2;
             for (int idx = threadIdx.x; idx < n * NV * D4; idx += blockDim.x) {
@@ -270,29 +271,29 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
                 delta_copy4(vdst + (tok * NV + v) * Dp + (d / kDeltaPer) * (kDeltaPer + kDeltaPad) + d % kDeltaPer, vecs + src);
             }
         }
-        float* wdst = val_sh + b * (kDeltaChunk * cols);
+        float* wdst = val_sh + b * (chunk * cols);
         for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
             const int tok = idx / cols, c = idx - tok * cols;
             if (col0 + c < V) delta_copy4(wdst + idx, vals + ((size_t)(c0 + tok) * H + h) * V + col0 + c);
         }
         if (MODE == 0) {
             for (int idx = threadIdx.x; idx < n * 2; idx += blockDim.x)
-                delta_copy4(scal_sh + b * (kDeltaChunk * 2) + idx, scal + (size_t)(c0 + idx / 2) * 2 * H + (size_t)(idx & 1) * H + h);
+                delta_copy4(scal_sh + b * (chunk * 2) + idx, scal + (size_t)(c0 + idx / 2) * 2 * H + (size_t)(idx & 1) * H + h);
         }
     };
     __syncthreads();                                // the zeros are in place before a copy lands among them
     if (t0 < t1) stage(0, t0);
     delta_copy_commit();
     int buf = 0;
-    for (int c0 = t0; c0 < t1; c0 += kDeltaChunk, buf ^= 1) {
-        const int n = min(kDeltaChunk, t1 - c0);
-        if (c0 + kDeltaChunk < t1) stage(buf ^ 1, c0 + kDeltaChunk);
+    for (int c0 = t0; c0 < t1; c0 += chunk, buf ^= 1) {
+        const int n = min(chunk, t1 - c0);
+        if (c0 + chunk < t1) stage(buf ^ 1, c0 + chunk);
         delta_copy_commit();
         delta_copy_wait_but_one();                  // this chunk's copies have landed; the next one's may fly
         __syncthreads();
-        const float* vec_b = vec_sh + buf * (kDeltaChunk * NV * Dp);
-        const float* val_b = val_sh + buf * (kDeltaChunk * cols);
-        const float* scal_b = scal_sh + buf * (kDeltaChunk * 2);
+        const float* vec_b = vec_sh + buf * (chunk * NV * Dp);
+        const float* val_b = val_sh + buf * (chunk * cols);
+        const float* scal_b = scal_sh + buf * (chunk * 2);
 #pragma unroll 2
         for (int tok = 0; tok < n; ++tok) {
             const float* vb = vec_b + tok * NV * Dp + part * (kDeltaPer + kDeltaPad);
@@ -589,13 +590,15 @@ LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const
     const int NV = mode == 0 ? 2 : 5;
     if (mode != 0) G = H;
     // walked columns -> threads of a block, blocks, shared memory
-    auto shape = [&](int columns, int* threads, dim3* grid, size_t* smem) {
+    auto shape = [&](int columns, int* threads, dim3* grid, size_t* smem, int* chunk) {
         int th = ((columns * split + 31) / 32) * 32;
         if (th > kDeltaThreads) th = kDeltaThreads;
         const int cols = th / split;
         *threads = th;
         *grid = dim3((columns + cols - 1) / cols, H, n_requests * max_segs);
+        *chunk = kDeltaChunk;
         *smem = (size_t)2 * kDeltaChunk * (NV * split * (kDeltaPer + kDeltaPad) + cols + 2) * sizeof(float);
+        if (*smem > 56 * 1024) { *chunk = kDeltaChunk / 2; *smem /= 2; }
     };
     const int Dr = ((D + 31) / 32) * 32;
     auto chain = [&](auto split_c) -> int {
@@ -608,8 +611,8 @@ LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const
     };
 #define LSB_DELTA_LAUNCH(MODE, SEG, COLUMNS)                                                                   \
     do {                                                                                                       \
-        int threads; dim3 grid; size_t smem;                                                                   \
-        shape(COLUMNS, &threads, &grid, &smem);                                                                \
+        int threads, chunk; dim3 grid; size_t smem;                                                            \
+        shape(COLUMNS, &threads, &grid, &smem, &chunk);                                                              \
         if (smem > 48 * 1024) {                                                                                \
             int rc = (int)cudaFuncSetAttribute(delta_scan_kernel<MODE, SEG>,                                   \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
@@ -617,7 +620,7 @@ LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const
         }                                                                                                      \
         int rc = lsb_launch(delta_scan_kernel<MODE, SEG>, grid, dim3(threads), smem, stream, 1, vecs, scal, vals, state, \
                             n_slots, q_start, table_rows, out, H, G, D, V, split, seg_len, max_segs, seg_acc,  \
-                            (const float*)seg_start);                                                          \
+                            (const float*)seg_start, chunk);                                                          \
         if (rc) return rc;                                                                                     \
     } while (0)
 #define LSB_DELTA_MODE(MODE)                                                                                   \
