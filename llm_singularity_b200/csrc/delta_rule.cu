@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(kDeltaThreads) channel_delta_prep_kernel(Chann
 //        segment's tokens write (E); D more columns start as the identity and take no writes, which
 //        leaves the product P of the segment's transitions (a token's step is linear in the state:
 //        S <- A_t S + k x^T, and a column of the identity walks through the same steps with x = 0).
-//        No outputs; E and P go to seg_acc [request * max_segs + segment, head, V + D, D].
+//        No outputs; E and P go to seg_acc [the segment's scratch row, head, V + D, D].
 // SEG 2: one segment from its start state (seg_start, laid out like the state), outputs only.
 // Between 1 and 2 delta_chain_kernel forms start(s + 1) = P_s start(s) + E_s segment after segment.
 // Three times the arithmetic of one walk, a chain a segment long.
@@ -212,9 +212,6 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     float* scal_sh = val_sh + 2 * chunk * cols;         // [2][chunk][2]
     const bool wide = (D & 3) == 0 && (reinterpret_cast<size_t>(vecs) & 15) == 0;
     lsb_pdl_launch_dependents();
-    // (channels past D and value columns past V are never staged: zero once, so that a lane's unused
-    // registers stay zero and the identity's columns meet no write)
-    for (int idx = threadIdx.x; idx < 2 * chunk * (NV * Dp + cols); idx += blockDim.x) vec_sh[idx] = 0.f;
     lsb_pdl_wait();
     const int r = SEG ? blockIdx.z / max_segs : blockIdx.z, sidx = SEG ? blockIdx.z % max_segs : 0;
     const int h = blockIdx.y;
@@ -223,6 +220,9 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
     const int col = col0 + lc;
     const int Vs = SEG == 1 ? V + D : V;            // columns walked
     int t0 = q_start[r], t1 = q_start[r + 1];
+    // (a request's segment s keeps its E, P and start in scratch row t0 / seg_len + r + s: rows of
+    // different requests never meet, and a step needs tokens / seg_len + requests rows at most)
+    const size_t zrow = SEG ? (size_t)(t0 / seg_len + r + sidx) : 0;
     if (SEG) {
         t0 += sidx * seg_len;
         if (t0 >= t1) return;                       // the request has fewer segments
@@ -233,10 +233,13 @@ delta_scan_kernel(const float* __restrict__ vecs, const float* __restrict__ scal
         if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
         return;
     }
+    // (channels past D and value columns past V are never staged: zero once, so that a lane's unused
+    // registers stay zero and the identity's columns meet no write)
+    for (int idx = threadIdx.x; idx < 2 * chunk * (NV * Dp + cols); idx += blockDim.x) vec_sh[idx] = 0.f;
     const bool live = col < Vs;
-    float* srow = SEG == 1 ? seg_acc + (((size_t)blockIdx.z * H + h) * Vs + (live ? col : 0)) * D
+    float* srow = SEG == 1 ? seg_acc + ((zrow * H + h) * Vs + (live ? col : 0)) * D
                            : state + (((size_t)slot * H + h) * V + (live ? col : 0)) * D;
-    const float* first = SEG == 2 ? seg_start + (((size_t)blockIdx.z * H + h) * V + (live ? col : 0)) * D : srow;
+    const float* first = SEG == 2 ? seg_start + ((zrow * H + h) * V + (live ? col : 0)) * D : srow;
     // (the state's share lives in pairs: the walk's arithmetic is the two-wide 32-bit FMA of sm_100,
     // one instruction for two channels, each channel rounded as the one-wide form rounds it)
     float2 s[kDeltaPer / 2];
@@ -422,7 +425,7 @@ delta_chain_kernel(float* __restrict__ state, int n_slots, const float* __restri
     for (int j = 0; j < kChainOwn; ++j) own[j] = (mine && my0 + j < V) ? srow[(size_t)(my0 + j) * D + d] : 0.f;
     __syncthreads();                                 // the zeros are in place
     for (int sg = 0; sg < n_seg; ++sg) {
-        const size_t z = (size_t)r * max_segs + sg;
+        const size_t z = (size_t)(q_start[r] / seg_len + r + sg);
         const float* E = seg_acc + (z * H + h) * Vs * D;
         const float* P = E + (size_t)V * D;
         float e[kChainOwn];
@@ -573,8 +576,8 @@ LSB_API int lsb_channel_delta_prep(const void* proj, int dtype, long long ld, in
 // mode 0: scalar gates (vecs [T, 2, G, D]: q then k; scal [T, 2, H]: fade then beta); mode 1: channel
 // gates (vecs [T, H, 5, D]: r, k, u, a * u, w).  vals [T, H, V]; state [slots, H, V, D]; out [T, H, V].
 // seg_len > 0 with scratch given and a portion longer than a segment: portions are walked in segments
-// side by side; seg_acc [requests * max_segs, H, V + D, D] and seg_start [requests * max_segs, H, V, D]
-// with max_segs = ceil(max_q_len / seg_len).
+// side by side; seg_acc [rows, H, V + D, D] and seg_start [rows, H, V, D] with rows = tokens / seg_len +
+// requests (segment s of the request that starts at token t0 uses row t0 / seg_len + request + s).
 LSB_API int lsb_delta_scan(int mode, const float* vecs, const float* scal, const float* vals, float* state, int n_slots,
                            const int* q_start, const int* table_rows, int n_requests, float* out, int H, int G, int D,
                            int V, int seg_len, int max_q_len, float* seg_acc, float* seg_start, cudaStream_t stream) {

@@ -1333,6 +1333,7 @@ def channel_delta_prep(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, h
 
 
 DELTA_SEGMENT = 128             # tokens of a segment when long portions of a delta-rule memory are walked in segments (0: never)
+DELTA_SEGMENT_REQUESTS = 64     # ... in steps of at most this many requests
 
 
 def delta_scan(form: str, vecs: torch.Tensor, scal: Optional[torch.Tensor], vals: torch.Tensor, state: torch.Tensor, ctx,
@@ -1359,12 +1360,14 @@ def delta_scan(form: str, vecs: torch.Tensor, scal: Optional[torch.Tensor], vals
             raise KernelError("delta_scan: scal must be [T, 2 * heads]")
     if key_dim > delta_max_key_dim():
         raise KernelError(f"delta_scan: key_dim {key_dim} is not supported (at most {delta_max_key_dim()})")
-    # a few requests with long portions: segments walked side by side (three times the arithmetic, a
-    # chain a segment long); many requests, short portions and single tokens: one walk each
+    # a step with a long portion: every request's tokens in segments walked side by side (three times the
+    # arithmetic, a chain a segment long), single tokens beside it included; short portions, single
+    # tokens only, or very many requests: one walk each.  Scratch: a row per segment,
+    # tokens / segment + requests at most.
     seg, seg_acc, seg_start = 0, None, None
-    if DELTA_SEGMENT and ctx.max_q_len >= 4 * DELTA_SEGMENT and ctx.n_requests <= 8:
+    if DELTA_SEGMENT and ctx.max_q_len >= 4 * DELTA_SEGMENT and ctx.n_requests <= DELTA_SEGMENT_REQUESTS:
         seg = DELTA_SEGMENT
-        n = ctx.n_requests * -(-ctx.max_q_len // seg)
+        n = T // seg + ctx.n_requests
         seg_acc = torch.empty(n * heads * (value_dim + key_dim) * key_dim, dtype=torch.float32, device=out.device)
         seg_start = torch.empty(n * heads * value_dim * key_dim, dtype=torch.float32, device=out.device)
     _call("delta_rule", "lsb_delta_scan", _i(0 if form == "scalar" else 1), _p(vecs), _p(scal if form == "scalar" else None),

@@ -461,6 +461,59 @@ def test_delta_walk_with_state_carried_and_slots_used_again(H, G, D, V, segment,
     K.check_status()
 
 
+@pytest.mark.parametrize("where", [0, 5, 12])
+def test_delta_walk_one_long_portion_beside_many_single_tokens(where, monkeypatch):
+    """Thirteen requests in one launch, one of them with a portion of 101 tokens (first, in the middle
+    or last in the batch) and the others with one to three tokens, every request from a state of its
+    own: the long portion is walked in segments of 16, the short ones ride along, and each request
+    matches a float64 walk of it alone.  Both forms."""
+    from llm_singularity_b200 import kernels as K
+    monkeypatch.setattr(K, "DELTA_SEGMENT", 16)
+    H, G, D, V = 4, 2, 24, 20
+    g = torch.Generator().manual_seed(where)
+    q_lens = [1 + (i % 3) for i in range(13)]
+    q_lens[where] = 101
+    rows = [(5 * i + 3) % 13 for i in range(13)]                  # the slots in another order than the batch
+    T = sum(q_lens)
+    ctx = _ctx(q_lens, [n + 7 for n in q_lens], rows=rows)
+    start = torch.randn(13, H, V, D, generator=g)                 # [slot, head, value, key]
+    k = _rand(T, G, D, g=g)
+    q = P.unit_length(_rand(T, G, D, g=g)) * D ** -0.5
+    fade, beta = torch.sigmoid(_rand(T, H, g=g) + 3.0), torch.sigmoid(_rand(T, H, g=g, scale=2.0))
+    v = _rand(T, H, V, g=g)
+    kh = _rand(T, H, D, g=g)
+    u = P.unit_length(kh)
+    au = torch.sigmoid(_rand(T, H, D, g=g, scale=2.0)) * u
+    w = torch.exp(-0.6 * torch.sigmoid(_rand(T, H, D, g=g, scale=2.0)))
+    rr, vd = _rand(T, H, D, g=g), _rand(T, H, D, g=g)
+    startd = torch.randn(13, H, D, D, generator=g)
+    for form in ("scalar", "channel"):
+        st0 = start if form == "scalar" else startd
+        state = st0.clone().cuda()
+        Vf = V if form == "scalar" else D
+        out = torch.empty(T, H * Vf, dtype=torch.float32, device="cuda")
+        f32 = lambda x: x.float().cuda().contiguous()
+        if form == "scalar":
+            vecs = torch.cat([f32(q).reshape(T, G * D), f32(P.unit_length(k)).reshape(T, G * D)], dim=1).contiguous()
+            K.delta_scan("scalar", vecs, torch.cat([f32(fade), f32(beta)], dim=1).contiguous(), f32(v).reshape(T, H * Vf),
+                         state, ctx, out, H, G, D, Vf)
+        else:
+            vecs = torch.stack([f32(x) for x in (rr, kh, u, au, w)], dim=2).contiguous()
+            K.delta_scan("channel", vecs, None, f32(vd).reshape(T, H * Vf), state, ctx, out, H, H, D, Vf)
+        t0 = 0
+        for i, n in enumerate(q_lens):
+            S = st0[rows[i]].double().transpose(1, 2).contiguous()        # [head, key, value]
+            sl = slice(t0, t0 + n)
+            want = _walk_scalar(S, q[sl], P.unit_length(k)[sl], v[sl], fade[sl], beta[sl]) if form == "scalar" \
+                else _walk_channel(S, rr[sl], kh[sl], u[sl], au[sl], w[sl], vd[sl])
+            got = out[sl].double().cpu().view(n, H, Vf)
+            scale = max(want.abs().max().item(), 1.0)
+            assert (got - want).abs().max() <= 2e-4 * scale, (form, i, n)
+            assert (state[rows[i]].double().cpu().transpose(1, 2) - S).abs().max() <= 2e-4 * max(S.abs().max().item(), 1.0), (form, i)
+            t0 += n
+    K.check_status()
+
+
 @pytest.mark.parametrize("segment", [None, 16])
 def test_delta_walk_reads_a_write_from_far_back(segment, monkeypatch):
     """Scalar form, no fading: token 2 writes value x under key e0 with full strength, every later
