@@ -212,6 +212,9 @@ struct AttnParams {
     float scale;
     int window;
     int skip_single;              // requests with one new token are left to the decode kernel
+    int sink;                     // one more place with score 0 and no value in every softmax
+    const bf16* gate;             // [tokens, heads] with this row stride: out *= sigmoid(gate), one number a head (or null)
+    long long gate_stride;
 };
 
 template <int HD>
@@ -560,7 +563,13 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             ok = warp_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1, &abort_flag, lane);
         }
         if (ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            // (the sink's share is 2^(0 - reference), the weight a key with score 0 would have had)
+            if (prm.sink) l += (m == -INFINITY) ? 1.f : exp2f(-m);
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (prm.gate != nullptr && live) {
+                const float z = __bfloat162float(prm.gate[(size_t)(qs + i0 + il) * prm.gate_stride + h]);
+                inv *= 1.f / (1.f + expf(-z));
+            }
             bf16* dst = prm.out + (size_t)(qs + i0 + il) * prm.nh * HD + (size_t)h * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -649,8 +658,8 @@ LSB_API int lsb_prefill_attention_tc5(const void* qkv, int qkv_stride, int n_tok
                                       const void* v_pages, const int* q_start, const int* kv_len,
                                       const int* table_rows, const int* block_table, int table_stride, void* out,
                                       int n_requests, int max_q_len, int nh, int nkv, int hd, int page_size,
-                                      int num_pages, float scale, int window, int skip_single,
-                                      cudaStream_t stream) {
+                                      int num_pages, float scale, int window, int skip_single, int sink,
+                                      const void* gate, long long gate_stride, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (!lsb_prefill_attention_tc5_supported(qkv, qkv_stride, k_pages, v_pages, nh, nkv, hd, page_size) ||
         n_requests > 65535 || (max_q_len + kRows - 1) / kRows > 65535)
@@ -675,6 +684,7 @@ LSB_API int lsb_prefill_attention_tc5(const void* qkv, int qkv_stride, int n_tok
     prm.q_start = q_start; prm.kv_len = kv_len; prm.table_rows = table_rows; prm.block_table = block_table;
     prm.table_stride = table_stride; prm.out = (bf16*)out; prm.nh = nh; prm.nkv = nkv;
     prm.page_size = page_size; prm.num_pages = num_pages; prm.scale = scale; prm.window = window; prm.skip_single = skip_single;
+    prm.sink = sink; prm.gate = (const bf16*)gate; prm.gate_stride = gate_stride;
     int sh = 0;
     while ((1 << sh) < page_size) ++sh;
     prm.page_shift = sh;

@@ -766,7 +766,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
             _call("attention_tc5", "lsb_prefill_attention_tc5", _p(qkv), _i(qkv.shape[1]), _i(T),
                   _p(cache.k_pages), _p(cache.v_pages), *per_request, _p(cache.block_table),
                   _i(cache.block_table.shape[1]), _p(out), _i(last - first), _i(ctx.max_q_len), *tail,
-                  skip, on)
+                  skip, _i(0), _p(None), _ll(0), on)
         else:
             _call("attention_tc", "lsb_prefill_attention", _p(qkv), _i(qkv.shape[1]), _p(cache.k_pages),
                   _p(cache.v_pages), *per_request, _p(cache.block_table), _i(cache.block_table.shape[1]),
@@ -1188,6 +1188,19 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
         gate_stride = gate.stride(0)
     flags = (1 if sink else 0) | (2 if gate is not None and gate_per_head else 0)
     _check_kv_cache(cache, nkv, dk, dv, q.dtype)
+    # a step of prompt portions only, equal key and value sizes, no chunks, no gate or one number a head:
+    # the tcgen05 prompt kernel, which takes the sink and that gate in its last step
+    if (USE_TCGEN05_ATTENTION and DV_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
+            and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128
+            and cache.page_size in (8, 16, 32, 64) and _batch_shape(ctx)[0] == 0
+            and _lib("attention_tc5").lsb_prefill_attention_tc5_supported(
+                _p(q), _i(q.shape[1]), _p(cache.k_pages), _p(cache.v_pages), _i(nh), _i(nkv), _i(dk), _i(cache.page_size))):
+        _call("attention_tc5", "lsb_prefill_attention_tc5", _p(q), _i(q.shape[1]), _i(T), _p(cache.k_pages),
+              _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table),
+              _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),
+              _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(0), _i(1 if sink else 0),
+              _p(gate), _ll(gate_stride), _stream(out))
+        return
     if (DV_TENSOR_CORES and q.dtype == torch.bfloat16 and gate_stride % 2 == 0
             and (gate is None or gate.data_ptr() % 4 == 0)
             and _lib("attention_dv").lsb_attention_dv_mma_supported(_i(dk), _i(dv))):

@@ -62,6 +62,10 @@ class KVAttention(Part):
             self.kernels = self.kernels + ("attention",)
             if rt.dtype == torch.bfloat16 and s.key_dim in (64, 128):
                 self.kernels = self.kernels + ("attention_tc", "attention_tc5")
+        elif (rt.dtype == torch.bfloat16 and s.key_dim == s.value_dim and s.key_dim in (64, 128) and s.chunk is None
+              and (not s.out_gate or self.gate_per_head)):
+            # steps of prompt portions only go to the tcgen05 prompt kernel, sink and gate per head included
+            self.kernels = self.kernels + ("attention_tc5",)
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:

@@ -295,6 +295,61 @@ def test_sink_attention_kernel_one_score_standing_out(dtype, nh, nkv, dk, dv, wi
     K.check_status()
 
 
+@pytest.mark.parametrize("nh, nkv, hd, window, page", [(4, 2, 128, 40, 16), (6, 1, 64, 1000, 16), (2, 2, 128, 129, 32),
+                                                       (8, 4, 64, 1, 8)])
+def test_sink_attention_of_prompt_only_steps(nh, nkv, hd, window, page, monkeypatch):
+    """A step without single tokens, equal key and value sizes, bfloat16: the route through the
+    tensor-memory prompt kernel (sink and gate per head in its last step) and the route through the
+    warp-level kernel both match plain arithmetic.  Three portions of 131 to 200 rows, two of them
+    continuing a longer sequence; one key per request stands out, just inside or just outside the
+    last query's window."""
+    from llm_singularity_b200 import kernels as K
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(hd + window)
+    q_lens, kv_lens = [150, 200, 131], [150, 260, 400]
+    ctx = _ctx(q_lens, kv_lens, rows=[1, 2, 0])
+    scale = 1.0 / math.sqrt(hd)
+    lows = [max(0, kv - window) for kv in kv_lens]
+    for targets in (lows, [max(lo - 1, 0) for lo in lows], [16, 127, 300]):
+        cache = _pages(3, 400, nkv, hd, hd, page, dtype, seed=2)
+        qs, outs = [], {True: [], False: []}
+        for r, (ql, kv, tgt) in enumerate(zip(q_lens, kv_lens, targets)):
+            Kd = 0.1 * torch.randn(kv, nkv, hd, generator=g)
+            Kd[tgt, :, 0] = 6.0
+            Vd = torch.randn(kv, nkv, hd, generator=g)
+            q = 0.1 * torch.randn(ql, nh, hd, generator=g)
+            q[:, :, 0] = 4.0 / scale
+            Kd, Vd, q = (t.to(dtype).double() for t in (Kd, Vd, q))
+            _fill(cache, [1, 2, 0][r], Kd, Vd)
+            pos = torch.arange(kv - ql, kv)[:, None]
+            keys = torch.arange(kv)[None, :]
+            ok = (keys <= pos) & (pos - keys < window)
+            for sink in (True, False):
+                o = torch.zeros(ql, nh, hd, dtype=F64)
+                for h in range(nh):
+                    sc = ((q[:, h] @ Kd[:, h // (nh // nkv)].T) * scale).masked_fill(~ok, float("-inf"))
+                    e = torch.exp(sc)
+                    o[:, h] = (e / (e.sum(-1, keepdim=True) + (1.0 if sink else 0.0))) @ Vd[:, h // (nh // nkv)]
+                outs[sink].append(o)
+            qs.append(q)
+        T = sum(q_lens)
+        q = torch.cat(qs).reshape(T, nh * hd).to(dtype).cuda()
+        gate = torch.randn(T, nh + 6, generator=g).to(dtype).cuda()
+        out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+        for tensor_memory in (True, False):
+            monkeypatch.setattr(K, "USE_TCGEN05_ATTENTION", tensor_memory)
+            for sink in (True, False):
+                out.zero_()
+                K.attention_dv(q, nh, nkv, hd, hd, ctx, cache, scale, window, 0, None, out, sink=sink)
+                want = torch.cat(outs[sink]).reshape(T, nh * hd)
+                assert (out.double().cpu() - want).abs().max() <= 8e-2, (targets, sink, tensor_memory)
+            out.zero_()
+            K.attention_dv(q, nh, nkv, hd, hd, ctx, cache, scale, window, 0, gate[:, 6:], out, sink=True, gate_per_head=True)
+            gated = (torch.cat(outs[True]) * torch.sigmoid(gate[:, 6:].double().cpu())[:, :, None]).reshape(T, nh * hd)
+            assert (out.double().cpu() - gated).abs().max() <= 8e-2, (targets, tensor_memory)
+    K.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sink_takes_everything_when_all_scores_are_low(dtype):
     """Scores of about -30 for every key: without the sink the output is the values' mean, with it
