@@ -72,7 +72,8 @@ def test_portions_of_any_size(tmp_path, dtype, name, n=150):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mix_a", "mix_c"])
 def test_long_portions_walked_in_segments(tmp_path, dtype, name, monkeypatch, n=150):
-    """The memories' long portions cut into segments of 16 and of 5 tokens that are walked side by side:
+    """The memories' long portions cut into segments of 16 and of 5 tokens (half as many for portions of
+    up to eight segments) that are walked side by side:
     a whole prompt, a long portion after a short one, and two long portions of unequal length in one
     batch, against the plain model."""
     from llm_singularity_b200 import kernels as K
