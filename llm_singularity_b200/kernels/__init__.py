@@ -1188,43 +1188,51 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
         gate_stride = gate.stride(0)
     flags = (1 if sink else 0) | (2 if gate is not None and gate_per_head else 0)
     _check_kv_cache(cache, nkv, dk, dv, q.dtype)
-    # a step of prompt portions only, equal key and value sizes, no chunks, no gate or one number a head:
-    # the tcgen05 prompt kernel, which takes the sink and that gate in its last step
+    # equal key and value sizes, no chunks, no gate or one number a head: the prompt portions of a step go
+    # to the tcgen05 prompt kernel, which takes the sink and that gate in its last step; single tokens,
+    # where they all come before the portions (as the scheduler puts them), go on below
+    n_req, max_q = ctx.n_requests, ctx.max_q_len
     if (USE_TCGEN05_ATTENTION and DV_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
             and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128
-            and cache.page_size in (8, 16, 32, 64) and _batch_shape(ctx)[0] == 0
+            and cache.page_size in (8, 16, 32, 64)
             and _lib("attention_tc5").lsb_prefill_attention_tc5_supported(
                 _p(q), _i(q.shape[1]), _p(cache.k_pages), _p(cache.v_pages), _i(nh), _i(nkv), _i(dk), _i(cache.page_size))):
-        _call("attention_tc5", "lsb_prefill_attention_tc5", _p(q), _i(q.shape[1]), _i(T), _p(cache.k_pages),
-              _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table),
-              _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),
-              _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(0), _i(1 if sink else 0),
-              _p(gate), _ll(gate_stride), _stream(out))
-        return
+        n_decode, first, last = _batch_shape(ctx)
+        if n_decode == 0 or (n_decode == first and last == ctx.n_requests):
+            off = 4 * first
+            _call("attention_tc5", "lsb_prefill_attention_tc5", _p(q), _i(q.shape[1]), _i(T), _p(cache.k_pages),
+                  _p(cache.v_pages), ctypes.c_void_p(ctx.q_start.data_ptr() + off),
+                  ctypes.c_void_p(ctx.kv_len.data_ptr() + off), ctypes.c_void_p(ctx.table_rows.data_ptr() + off),
+                  _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests - first),
+                  _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale),
+                  _i(window), _i(0), _i(1 if sink else 0), _p(gate), _ll(gate_stride), _stream(out))
+            if first == 0:
+                return
+            n_req, max_q = first, 1
     if (DV_TENSOR_CORES and q.dtype == torch.bfloat16 and gate_stride % 2 == 0
             and (gate is None or gate.data_ptr() % 4 == 0)
             and _lib("attention_dv").lsb_attention_dv_mma_supported(_i(dk), _i(dv))):
         # a few blocks only (single tokens, one short portion): the keys of a row tile are shared among
         # several blocks, whose partial sums meet in a scratch buffer kept for reuse
         lib = _lib("attention_dv")
-        plan = lib.lsb_attention_dv_mma_plan(_i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(chunk),
+        plan = lib.lsb_attention_dv_mma_plan(_i(n_req), _i(max_q), _i(nh), _i(nkv), _i(chunk),
                                              _i(num_sms(q.device)), _i(DV_BLOCK_SHAPE))
         scratch = None
         if plan >> 8 > 1:
-            tiles = -(-ctx.max_q_len * (nh // nkv) // 16)
-            key = ("attention_dv", q.device, ctx.n_requests * nkv * tiles * (plan >> 8) * 16 * (dv + 2))
+            tiles = -(-max_q * (nh // nkv) // 16)
+            key = ("attention_dv", q.device, n_req * nkv * tiles * (plan >> 8) * 16 * (dv + 2))
             scratch = _scratch.get(key)
             if scratch is None:
                 scratch = _scratch[key] = torch.empty(key[2], dtype=torch.float32, device=q.device)
         _call("attention_dv", "lsb_attention_dv_mma", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
               _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
-              _ll(gate_stride), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(dv),
+              _ll(gate_stride), _p(out), _i(n_req), _i(max_q), _i(nh), _i(nkv), _i(dk), _i(dv),
               _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(num_sms(q.device)),
               _i(DV_BLOCK_SHAPE), _p(scratch), _i(flags), _stream(out))
         return
     _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
           _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
-          _ll(gate_stride), _p(out), _i(_dt(q)), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),
+          _ll(gate_stride), _p(out), _i(_dt(q)), _i(n_req), _i(max_q), _i(nh), _i(nkv), _i(dk),
           _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(flags), _stream(out))
 
 

@@ -99,6 +99,33 @@ def test_long_portions_walked_in_segments(tmp_path, dtype, name, monkeypatch, n=
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_long_portions_beside_single_tokens(tmp_path, dtype, name="mix_b"):
+    """Portions of 140 to 150 tokens in one step with another request's single token, the single token
+    before the portion and after it (the attention layers with equal key and value sizes send such
+    portions to another kernel than single tokens and short portions), against the plain model of
+    each request alone."""
+    from llm_singularity_b200.engine.batch import StepEntry
+    cfg = U.CONFIGS[name]
+    W, path = _setup(tmp_path, cfg, 13, rank=U.DECAY_RANKS[name])
+    x, y = U.tokens_for(cfg, 300, 6), U.tokens_for(cfg, 170, 7)
+    want_x, want_y = U.plain_logits(cfg, W, x), U.plain_logits(cfg, W, y)
+    r = U.make_runner(path, dtype, pages=40)
+    assert r.open("x") and r.open("y")
+    every = lambda n: list(range(n))
+    a = r.step([StepEntry("y", y[:139], every(139))]).float().cpu()
+    b = r.step([StepEntry("y", y[139:140], [0]), StepEntry("x", x[:150], every(150))]).float().cpu()
+    c = r.step([StepEntry("x", x[150:290], every(140)), StepEntry("y", y[140:141], [0])]).float().cpu()
+    d = r.step([StepEntry("y", y[141:], every(29)), StepEntry("x", x[290:], every(10))]).float().cpu()
+    r.close("x"); r.close("y")
+    r.check_kernels()
+    got_x = torch.cat([b[1:], c[:140], d[29:]])
+    got_y = torch.cat([a, b[:1], c[140:], d[:29]])
+    assert U.close(got_x, want_x, dtype), U.rel_err(got_x, want_x)
+    assert U.close(got_y, want_y, dtype), U.rel_err(got_y, want_y)
+    r.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mix_a", "mix_b", "mix_c"])
 def test_mixed_batches_with_slots_and_pages_used_again(tmp_path, dtype, name):
     """Four requests of unequal length stepped together (portions beside single tokens, a request
@@ -298,21 +325,25 @@ def test_sink_attention_kernel_one_score_standing_out(dtype, nh, nkv, dk, dv, wi
 
 @pytest.mark.parametrize("nh, nkv, hd, window, page", [(4, 2, 128, 40, 16), (6, 1, 64, 1000, 16), (2, 2, 128, 129, 32),
                                                        (8, 4, 64, 1, 8)])
-def test_sink_attention_of_prompt_only_steps(nh, nkv, hd, window, page, monkeypatch):
-    """A step without single tokens, equal key and value sizes, bfloat16: the route through the
-    tensor-memory prompt kernel (sink and gate per head in its last step) and the route through the
-    warp-level kernel both match plain arithmetic.  Three portions of 131 to 200 rows, two of them
-    continuing a longer sequence; one key per request stands out, just inside or just outside the
-    last query's window."""
+@pytest.mark.parametrize("singles", [0, 2])
+def test_sink_attention_of_steps_with_long_portions(nh, nkv, hd, window, page, singles, monkeypatch):
+    """Equal key and value sizes, bfloat16: the route through the tensor-memory prompt kernel (sink and
+    gate per head in its last step; single tokens that come first in the step go through the
+    warp-level kernel in the same call) and the route through the warp-level kernel alone both match
+    plain arithmetic.  Three portions of 131 to 200 rows, two of them continuing a longer sequence,
+    with or without two single tokens before them; one key per request stands out, just inside or
+    just outside the last query's window."""
     from llm_singularity_b200 import kernels as K
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(hd + window)
-    q_lens, kv_lens = [150, 200, 131], [150, 260, 400]
-    ctx = _ctx(q_lens, kv_lens, rows=[1, 2, 0])
+    q_lens, kv_lens, rows = [150, 200, 131], [150, 260, 400], [1, 2, 0]
+    if singles:
+        q_lens, kv_lens, rows = [1, 1] + q_lens, [77, 300] + kv_lens, [4, 3] + rows
+    ctx = _ctx(q_lens, kv_lens, rows=rows)
     scale = 1.0 / math.sqrt(hd)
     lows = [max(0, kv - window) for kv in kv_lens]
-    for targets in (lows, [max(lo - 1, 0) for lo in lows], [16, 127, 300]):
-        cache = _pages(3, 400, nkv, hd, hd, page, dtype, seed=2)
+    for targets in (lows, [max(lo - 1, 0) for lo in lows], [min(t, kv - 1) for t, kv in zip([40, 127, 16, 127, 300][-len(q_lens):], kv_lens)]):
+        cache = _pages(5, 400, nkv, hd, hd, page, dtype, seed=2)
         qs, outs = [], {True: [], False: []}
         for r, (ql, kv, tgt) in enumerate(zip(q_lens, kv_lens, targets)):
             Kd = 0.1 * torch.randn(kv, nkv, hd, generator=g)
@@ -321,7 +352,7 @@ def test_sink_attention_of_prompt_only_steps(nh, nkv, hd, window, page, monkeypa
             q = 0.1 * torch.randn(ql, nh, hd, generator=g)
             q[:, :, 0] = 4.0 / scale
             Kd, Vd, q = (t.to(dtype).double() for t in (Kd, Vd, q))
-            _fill(cache, [1, 2, 0][r], Kd, Vd)
+            _fill(cache, rows[r], Kd, Vd)
             pos = torch.arange(kv - ql, kv)[:, None]
             keys = torch.arange(kv)[None, :]
             ok = (keys <= pos) & (pos - keys < window)
