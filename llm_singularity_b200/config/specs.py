@@ -47,6 +47,16 @@ class GroupRMSNormSpec(PartSpec):
     kind: str = field(init=False, default="group_rmsnorm")
 
 
+@dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """``(x - mean) / sqrt(var + eps) * w + b`` with ``var`` the mean of the squared deviations: a
+    centred norm with a weight and a bias."""
+
+    size: int = 0
+    eps: float = 1e-5
+    kind: str = field(init=False, default="layernorm")
+
+
 # ---------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class Llama3RopeScaling:
@@ -137,7 +147,12 @@ class KVAttentionSpec(PartSpec):
     norm over all heads at once, before they are split, with a weight as long as the projection.
     ``v_unit_norm``: each value head is divided by its root mean square (``eps``, no weight) and
     cached so.  ``sink``: one is added to the softmax's denominator, a place with score 0 and no
-    value, so that a row's weights may sum to less than one."""
+    value, so that a row's weights may sum to less than one.  ``logit_softcap``: a scaled score s
+    becomes ``cap * tanh(s / cap)``.  ``linear_bias``: head h's score for a key d positions back then
+    loses ``2^(-8 (h + 1) / heads) * d``.  ``value_mix``: layers of one model that name the same
+    ``value_mix_key`` share values within a token; the "source" layer (the first of them) caches its
+    values as they are and lends them to the others for the step, a "mixed" layer caches
+    ``(1 - lambda) v + lambda v_source`` with its own learnt number ``vmix``."""
 
     hidden_size: int = 0
     num_heads: int = 0
@@ -147,6 +162,10 @@ class KVAttentionSpec(PartSpec):
     scale: float = 0.0
     window: Optional[int] = None
     chunk: Optional[int] = None
+    logit_softcap: Optional[float] = None
+    linear_bias: bool = False
+    value_mix: Optional[str] = None
+    value_mix_key: str = "v_first"
     qkv_bias: bool = False
     qk_norm: bool = False
     eps: float = 1e-5
@@ -253,7 +272,8 @@ class LatentAttentionSpec(PartSpec):
     """Causal softmax attention whose keys and values are made per head from one cached latent
     vector per token, plus one rotated key part that all heads share.  Queries come through a
     normed latent of their own.  ``reads_only``: the layer has no latent projection and reads
-    the cache another layer of the same shape writes."""
+    the cache another layer of the same shape writes.  ``gate_per_head``: head h's output is
+    multiplied by ``sigmoid(W_g x)_h``, W_g with one row per head."""
 
     hidden_size: int = 0
     num_heads: int = 0
@@ -266,17 +286,39 @@ class LatentAttentionSpec(PartSpec):
     eps: float = 1e-5
     reads_only: bool = False
     position: PartSpec = field(default_factory=NoPositionSpec)
+    gate_per_head: bool = False
     kind: str = field(init=False, default="latent_attention")
+
+
+@dataclass(frozen=True)
+class RGLRUSpec(PartSpec):
+    """A recurrent block with a real-gated linear recurrent unit.  Two branches of ``width``:
+    ``y = gelu_tanh(W_y x + b_y)`` and ``u = conv(W_x x + b_x)``, a causal convolution per channel over
+    ``conv_taps`` tokens with a bias.  u is cut into ``blocks`` equal parts; in part b
+    ``r = sigmoid(R_b u_b + b_r)`` and ``i = sigmoid(I_b u_b + b_i)`` with square matrices R_b, I_b.  Then
+
+        a = exp(-rate * r * softplus(lam));   S <- a S + sqrt(1 - a^2) * i * u;   out = W_o (S * y)
+
+    with S zero when a sequence begins, one number per channel, 32-bit."""
+
+    hidden_size: int = 0
+    width: int = 0
+    blocks: int = 1
+    conv_taps: int = 1
+    rate: float = 8.0
+    kind: str = field(init=False, default="rglru")
 
 
 # -------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
-    """down( act(gate(x)) * up(x) ), dense, no bias."""
+    """down( act(gate(x)) * up(x) ), dense, no bias.  ``activation`` "capped_glu" with ``limit`` L is
+    ``min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1)`` for gate g and up u."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    limit: float = 0.0
     kind: str = field(init=False, default="gated_mlp")
 
 
@@ -300,7 +342,11 @@ class MoESpec(PartSpec):
     Router logits are 32-bit; ``score`` turns them into scores ("sigmoid", or "softmax" over all
     experts); the ``top`` largest are chosen; ``renormalize`` divides the chosen scores by their
     sum.  ``weight_on`` says what a score multiplies: the expert's "input" (``u = s x``) or its
-    "output"."""
+    "output".  ``choice_bias``: a learnt number per expert is added to the scores for the choice only
+    (the weights are the scores without it).  The chosen scores are divided by their sum +
+    ``renorm_eps`` and multiplied by ``weight_scale``.  ``limit`` belongs to the activation
+    "capped_glu" (see ``GatedMLPSpec``).  ``shared``: a gated feed-forward that every token passes
+    besides its chosen experts; its result is added."""
 
     hidden_size: int = 0
     expert_size: int = 0
@@ -310,6 +356,11 @@ class MoESpec(PartSpec):
     score: str = "sigmoid"
     renormalize: bool = False
     weight_on: str = "input"
+    choice_bias: bool = False
+    weight_scale: float = 1.0
+    renorm_eps: float = 0.0
+    limit: float = 0.0
+    shared: Optional[GatedMLPSpec] = None
     kind: str = field(init=False, default="moe")
 
 
@@ -400,6 +451,11 @@ class EmbeddingSpec(PartSpec):
     hidden_size: int = 0
     side_size: int = 0            # columns of a second table of per-token inputs for the blocks (0: none)
     scale: float = 1.0            # multiplies the looked-up row on its way into the stream
+    # a second table of ``pair_buckets`` + 1 rows, added: row (previous token * pair_mul_prev + token *
+    # pair_mul_cur) mod pair_buckets, the last row for a sequence's first token (0 buckets: no such table)
+    pair_buckets: int = 0
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
     kind: str = field(init=False, default="embedding")
 
 

@@ -9,6 +9,8 @@
 // weighted sum of values is divided by the sum at the end and, if a gate is given, multiplied by
 // sigmoid(gate[t, h * dv + c]) on the way out.  Keys are [page][kv head][offset][dk], values
 // [page][kv head][offset][dv].  Scores, weights and sums are 32-bit.  Two options ride in `flags`:
+// kDvLinearBias takes slope_h * (p - j) off the score of key j for the query at p, slope_h = 2^(-8 (h + 1) / nh);
+// `softcap` > 0 replaces a scaled score s by softcap * tanh(s / softcap) before that.
 // kDvSink adds one to the softmax's denominator (a place with score 0 and no value, so a row's weights
 // sum to less than one), kDvGateHeads reads one gate number per head, gate[t, h], instead of one per
 // output channel.
@@ -36,7 +38,7 @@ LSB_DEFINE_STATUS()
 
 constexpr int kDvWarps = 4;
 constexpr int kDvMaxDim = 256;
-constexpr int kDvSink = 1, kDvGateHeads = 2;
+constexpr int kDvSink = 1, kDvGateHeads = 2, kDvLinearBias = 4;
 
 template <typename T>
 __device__ __forceinline__ float dv_dot(const float* __restrict__ q, const T* __restrict__ k, int n, bool vec) {
@@ -71,7 +73,7 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
                             const int* __restrict__ table_rows, const int* __restrict__ block_table, int table_stride,
                             const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
                             int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
-                            int chunk, int vec, int flags) {
+                            int chunk, int vec, int flags, float softcap) {
     __shared__ float q_sh[kDvWarps][kDvMaxDim];
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
@@ -92,6 +94,7 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
     const T* qr = q + ((size_t)t * nh + h) * dk;
     for (int d = lane; d < dk; d += 32) q_sh[warp][d] = lsb_to_float(qr[d]) * scale;
     __syncwarp();
+    const float slope = (flags & kDvLinearBias) ? exp2f(-8.f * (float)(h + 1) / (float)nh) : 0.f;
 
     constexpr int kAccs = kDvMaxDim / 32;
     float acc[kAccs];
@@ -110,6 +113,8 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
             } else {
                 at = ((long long)page * nkv + g) * page_size + (kj % page_size);
                 s = dv_dot<T>(q_sh[warp], k_pages + at * dk, dk, vec != 0);
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+                s -= slope * (float)(p - kj);
             }
         }
         const float m_new = fmaxf(m, lsb_warp_max(s));
@@ -175,7 +180,7 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ gate, long long gate_stride,
                         __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
                         int num_pages, float scale_log2, int window, int chunk, int ksplit, float* __restrict__ scratch,
-                        int flags) {
+                        int flags, float scale, float softcap) {
     constexpr int KS = DKP + 8, VS = DVP + 8;          // row strides in elements: 4 words past a multiple of 32
     extern __shared__ __align__(16) unsigned char dv_smem[];
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(dv_smem);       // [STAGES][64][KS]
@@ -224,6 +229,10 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int h_a = g * group + row_a % group, h_b = g * group + row_b % group;
     const size_t t_a = (size_t)qs + row_a / group, t_b = (size_t)qs + row_b / group;
     const int dk_steps = dk >> 4, dv_blocks = dv >> 3;
+    // scores that are capped or carry a bias growing with the distance leave the base-2 form for a moment
+    const bool modified = softcap > 0.f || (flags & kDvLinearBias) != 0;
+    const float slope_a = (flags & kDvLinearBias) ? exp2f(-8.f * (float)(h_a + 1) / (float)nh) : 0.f;
+    const float slope_b = (flags & kDvLinearBias) ? exp2f(-8.f * (float)(h_b + 1) / (float)nh) : 0.f;
 
     uint32_t qa[DKP / 16][4];
     {
@@ -325,7 +334,20 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             }
             const int tile_key0 = kt * kMmaKeys + key0;
             const bool interior = slab_full && tile_key0 >= slab_lo && tile_key0 + NJ * 8 - 1 <= slab_hi;
-            if (interior) {
+            if (modified) {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = tile_key0 + j * 8 + 2 * tid4 + (e & 1);
+                        const bool ok = e < 2 ? (ok_a && key >= lo_a && key <= pos_a) : (ok_b && key >= lo_b && key <= pos_b);
+                        float v = s[j][e] * scale;
+                        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+                        v -= e < 2 ? slope_a * (float)(pos_a - key) : slope_b * (float)(pos_b - key);
+                        s[j][e] = ok ? v * 1.4426950408889634f : -FLT_MAX;
+                    }
+                }
+            } else if (interior) {
 #pragma unroll
                 for (int j = 0; j < NJ; ++j) {
 #pragma unroll
@@ -572,7 +594,8 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
                                  const int* kv_len, const int* table_rows, const int* block_table, int table_stride,
                                  const void* gate, long long gate_stride, void* out, int n_requests, int max_q_len,
                                  int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
-                                 int chunk, int sms, int shape, float* scratch, int flags, cudaStream_t stream) {
+                                 int chunk, int sms, int shape, float* scratch, int flags, float softcap,
+                                 cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (sms <= 0) sms = 148;
     if (!lsb_attention_dv_mma_supported(dk, dv) || nkv <= 0 || nh % nkv || window < 0 || chunk < 0 || n_requests > 65535 ||
@@ -599,7 +622,7 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
                           stream, 1, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,                     \
                           (const __nv_bfloat16*)v_pages, q_start, kv_len, table_rows, block_table, table_stride, \
                           (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, nh, nkv, dk, dv,         \
-                          page_size, num_pages, scale_log2, window, chunk, ksplit, scratch, flags);              \
+                          page_size, num_pages, scale_log2, window, chunk, ksplit, scratch, flags, scale, softcap);              \
     } while (0)
 #define LSB_DV_MMA_SHAPE(DKP, DVP)                                                                               \
     do {                                                                                                         \
@@ -633,7 +656,8 @@ LSB_API int lsb_attention_dv_generic(const void* q, const void* k_pages, const v
                                      const int* kv_len, const int* table_rows, const int* block_table,
                                      int table_stride, const void* gate, long long gate_stride, void* out, int dtype,
                                      int n_requests, int max_q_len, int nh, int nkv, int dk, int dv, int page_size,
-                                     int num_pages, float scale, int window, int chunk, int flags, cudaStream_t stream) {
+                                     int num_pages, float scale, int window, int chunk, int flags, float softcap,
+                                     cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (dk <= 0 || dk > kDvMaxDim || dv <= 0 || dv > kDvMaxDim || nkv <= 0 || nh % nkv || window < 0 || chunk < 0)
         return (int)cudaErrorInvalidValue;
@@ -644,6 +668,6 @@ LSB_API int lsb_attention_dv_generic(const void* q, const void* k_pages, const v
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
         attention_dv_generic_kernel<T>, grid, dim3(kDvWarps * 32), 0, stream, 1, (const T*)q, (const T*)k_pages,
         (const T*)v_pages, q_start, kv_len, table_rows, block_table, table_stride, (const T*)gate, gate_stride,
-        (T*)out, nh, nkv, dk, dv, page_size, num_pages, scale, window, chunk, vec, flags));
+        (T*)out, nh, nkv, dk, dv, page_size, num_pages, scale, window, chunk, vec, flags, softcap));
     return 0;
 }

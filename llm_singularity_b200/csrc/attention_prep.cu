@@ -6,6 +6,9 @@
 //     all heads of q and one for all heads of k; or (`norm_all`) one norm over all heads of q at
 //     once and one over all heads of k, with weights as long as the whole projection;
 //   * each value head divided by its root mean square (`v_unit`: no weight, the same eps);
+//   * values mixed with those another layer made of the same token in this step (`v_first`, rows of
+//     `v_first_ld` elements in the compute dtype): v <- (1 - lambda) v + lambda v_first, lambda one
+//     32-bit number on the device; the mixed values are what is cached;
 //   * a query temperature: q *= 1 + coef * ln(floor((pos + 1) / every) + 1);
 //   * rotation of the first `rotary_dim` dims of every q and k head by pos * inv_freq[i], pairs
 //     (2i, 2i + 1) ("adjacent") or (i, i + rotary_dim / 2) ("half"), angle formed in 32-bit;
@@ -33,6 +36,7 @@ struct PrepArgs {
     const float* inv_freq; int rotary_dim, adjacent;
     const int *positions, *token_req, *table_rows, *block_table; int table_stride;
     void *q_out, *k_pages, *v_pages; int page_size, num_pages, store;
+    const void* v_first; long long v_first_ld; const float* v_lambda;
     int vec;        // 16-byte loads of the projections: every offset, ld, dk and dv a multiple of 16 bytes
 };
 
@@ -225,7 +229,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
                 ((T*)a.v_pages)[v_base + (long long)head * a.page_size * a.dv + d] = lsb_from_float<T>(x * inv);
             }
         }
-    } else if (v_base >= 0 && a.vec && !a.v_bias) {
+    } else if (v_base >= 0 && a.vec && !a.v_bias && !a.v_first) {
         const T* v = row + a.v_off;
         for (int w = threadIdx.x * VEC; w < a.nkv * a.dv; w += blockDim.x * VEC) {
             const int head = w / a.dv, d = w - head * a.dv;
@@ -238,6 +242,10 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
             const int head = w / a.dv, d = w - head * a.dv;
             float x = lsb_to_float(v[w]);
             if (a.v_bias) x += a.v_bias[w];
+            if (a.v_first) {
+                const float lam = a.v_lambda[0];
+                x = (1.f - lam) * x + lam * lsb_to_float(((const T*)a.v_first)[(size_t)t * a.v_first_ld + w]);
+            }
             ((T*)a.v_pages)[v_base + (long long)head * a.page_size * a.dv + d] = lsb_from_float<T>(x);
         }
     }
@@ -251,10 +259,11 @@ LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_
                                int norm_all, int v_unit, float temp_coef, int temp_every, const float* inv_freq, int rotary_dim, int adjacent,
                                const int* positions, const int* token_req, const int* table_rows,
                                const int* block_table, int table_stride, void* q_out, void* k_pages, void* v_pages,
-                               int page_size, int num_pages, int store, cudaStream_t stream) {
+                               int page_size, int num_pages, int store, const void* v_first, long long v_first_ld,
+                               const float* v_lambda, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dk <= 0 || dk > kPrepMaxDim || dv <= 0 || nh <= 0 || nkv <= 0 || rotary_dim % 2 || rotary_dim > dk ||
-        rotary_dim < 0 || (rotary_dim > 0 && !inv_freq))
+        rotary_dim < 0 || (rotary_dim > 0 && !inv_freq) || (v_first && (!v_lambda || v_unit)))
         return (int)cudaErrorInvalidValue;
     PrepArgs a;
     a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
@@ -268,6 +277,7 @@ LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_
     a.table_stride = table_stride;
     a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.page_size = page_size; a.num_pages = num_pages;
     a.store = store;
+    a.v_first = v_first; a.v_first_ld = v_first_ld; a.v_lambda = v_lambda;
     const int per16 = dtype == LSB_F32 ? 4 : 8;
     a.vec = ((uintptr_t)proj % 16 == 0 && (uintptr_t)v_pages % 16 == 0 && ld % per16 == 0 && q_off % per16 == 0 &&
              k_off % per16 == 0 && v_off % per16 == 0 && dk % per16 == 0 && dv % per16 == 0) ? 1 : 0;

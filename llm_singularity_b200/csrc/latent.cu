@@ -288,3 +288,30 @@ LSB_API int lsb_latent_attention(const float* qf, const void* pages, int dtype, 
         page_size, num_pages, scale));
     return 0;
 }
+
+// A gate of one number per head on the heads' outputs, in place: x[t, h, :] *= sigmoid(gate[t, h]), the
+// gate numbers 32-bit in rows of `gate_ld` (they come out of the same product as the latents).
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const float* __restrict__ gate, long long gate_ld, int heads,
+                                 int dim, long long total) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long th = i / dim;
+        const long long t = th / heads;
+        const int h = (int)(th - t * heads);
+        const float g = 1.f / (1.f + expf(-gate[t * gate_ld + h]));
+        x[i] = lsb_from_float<T>(lsb_to_float(x[i]) * g);
+    }
+}
+
+LSB_API int lsb_head_gate(void* x, int dtype, const float* gate, long long gate_ld, int tokens, int heads, int dim,
+                          cudaStream_t stream) {
+    const long long total = (long long)tokens * heads * dim;
+    if (total <= 0) return 0;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(head_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, 1, (T*)x, gate,
+                                                gate_ld, heads, dim, total));
+    return 0;
+}

@@ -23,17 +23,33 @@ LSB_DEFINE_STATUS()
 
 constexpr int kTile = 32;               // rows per tile; an expert's rows are padded to this
 
-__device__ __forceinline__ float moe_act(float z, int act) {
-    if (act == 1) return z / (1.f + expf(-z));
-    if (act == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    return z;
+// act(g) * u of a gated expert; act 5 is the capped form with a limit L: min(g, L) sigmoid(1.702 min(g, L))
+// (clamp(u, -L, L) + 1)
+__device__ __forceinline__ float moe_gate_mul(float z, float up, int act, float limit) {
+    if (act == 5) {
+        const float g = fminf(z, limit);
+        return g / (1.f + expf(-1.702f * g)) * (fminf(fmaxf(up, -limit), limit) + 1.f);
+    }
+    if (act == 1) return z / (1.f + expf(-z)) * up;
+    if (act == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) * up;
+    return z * up;
 }
+
+// How scores are made and weighted: `score` 0 sigmoid, 1 softmax over all experts; `bias` (one number an
+// expert, may be null) is added to the scores for the choice only; the chosen scores are divided by
+// their sum + eps if `renorm`, and multiplied by `scale`.
+struct RouteOpts {
+    int score, renorm;
+    const float* bias;
+    float scale, eps;
+};
 
 constexpr int kMaxTop = 32;
 
 // One warp chooses for one token (all lanes call it together).
-__device__ __forceinline__ void route_token(const float* __restrict__ z, int E, int top, int score, int renorm,
+__device__ __forceinline__ void route_token(const float* __restrict__ z, int E, int top, const RouteOpts ro,
                                             int* __restrict__ ids, float* __restrict__ wts, int lane) {
+    const int score = ro.score, renorm = ro.renorm;
     float zmax = -FLT_MAX, denom = 1.f;
     if (score == 1) {
         for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
@@ -51,7 +67,9 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z, int E, 
         for (int e = lane; e < E; e += 32) {
             bool taken = false;
             for (int j = 0; j < k; ++j) taken |= (chosen[j] == e);
-            if (!taken && (z[e] > best || (z[e] == best && e < bi))) { best = z[e]; bi = e; }
+            // (without a bias the logits order the experts as their scores do)
+            const float c = ro.bias ? (score == 1 ? expf(z[e] - zmax) / denom : 1.f / (1.f + expf(-z[e]))) + ro.bias[e] : z[e];
+            if (!taken && (c > best || (c == best && e < bi))) { best = c; bi = e; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -60,31 +78,32 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z, int E, 
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
         chosen[k] = bi;
+        if (ro.bias) best = z[bi];
         val[k] = score == 1 ? expf(best - zmax) / denom : 1.f / (1.f + expf(-best));
         total += val[k];
     }
     if (lane == 0) {
         for (int k = 0; k < top; ++k) {
             ids[k] = chosen[k];
-            wts[k] = renorm ? val[k] / total : val[k];
+            wts[k] = (renorm ? val[k] / (total + ro.eps) : val[k]) * ro.scale;
         }
     }
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
-                                 int score, int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+                                 RouteOpts ro, int* __restrict__ ids, float* __restrict__ wts) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_tokens) return;
-    route_token(logits + (size_t)warp * E, E, top, score, renorm, ids + (size_t)warp * top, wts + (size_t)warp * top, lane);
+    route_token(logits + (size_t)warp * E, E, top, ro, ids + (size_t)warp * top, wts + (size_t)warp * top, lane);
 }
 
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(int* __restrict__ ids, float* __restrict__ wts, int n, int top, int E,
                  int cap_tiles, int tile, int* __restrict__ pos, int* __restrict__ row_token,
                  float* __restrict__ row_scale, int* __restrict__ tile_expert,
-                 const float* __restrict__ logits, int score, int renorm) {
+                 const float* __restrict__ logits, RouteOpts ro) {
     extern __shared__ int shi[];
     int* counts = shi;                  // E
     int* starts = shi + E;              // E + 1, in rows
@@ -92,7 +111,7 @@ moe_align_kernel(int* __restrict__ ids, float* __restrict__ wts, int n, int top,
     lsb_pdl_wait();
     if (logits) {                       // a step of few tokens: the choosing is done here too, a warp a token
         for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5)
-            route_token(logits + (size_t)t * E, E, top, score, renorm, ids + (size_t)t * top, wts + (size_t)t * top,
+            route_token(logits + (size_t)t * E, E, top, ro, ids + (size_t)t * top, wts + (size_t)t * top,
                         threadIdx.x & 31);
         __syncthreads();
     }
@@ -133,7 +152,7 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ A, const int* __restrict__ row_token,
                 const float* __restrict__ row_scale, int on_input, const T* __restrict__ W,
-                const int* __restrict__ tile_expert, void* __restrict__ out_, int N, int K, int act) {
+                const int* __restrict__ tile_expert, void* __restrict__ out_, int N, int K, int act, float limit) {
     __shared__ float As[kTile][kTile + 1];
     __shared__ float Bs[kTile][kTile + 1];
     __shared__ int tok_sh[kTile];
@@ -180,7 +199,7 @@ moe_gemm_kernel(const T* __restrict__ A, const int* __restrict__ row_token,
         if (MODE == 0) {
             const float up = __shfl_down_sync(0xffffffffu, acc[j], 1);
             if (!(tx & 1) && n + 1 < N)
-                ((T*)out_)[(size_t)m * (N / 2) + n / 2] = lsb_from_float<T>(moe_act(acc[j], act) * up);
+                ((T*)out_)[(size_t)m * (N / 2) + n / 2] = lsb_from_float<T>(moe_gate_mul(acc[j], up, act, limit));
         } else if (n < N) {
             ((float*)out_)[(size_t)m * N + n] = acc[j];
         }
@@ -242,25 +261,27 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 LSB_API int lsb_moe_tile() { return kTile; }
 
 LSB_API int lsb_moe_route(const float* logits, int n_tokens, int E, int top, int score, int renorm,
-                          int* ids, float* wts, cudaStream_t stream) {
+                          const float* bias, float scale, float eps, int* ids, float* wts, cudaStream_t stream) {
+    const RouteOpts ro = {score, renorm, bias, scale, eps};
     if (n_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > kMaxTop || score < 0 || score > 1) return (int)cudaErrorInvalidValue;
     const int warps_per_block = 4;
     return lsb_launch(moe_route_kernel, dim3((n_tokens + warps_per_block - 1) / warps_per_block),
-                      dim3(32 * warps_per_block), 0, stream, 1, logits, n_tokens, E, top, score, renorm, ids, wts);
+                      dim3(32 * warps_per_block), 0, stream, 1, logits, n_tokens, E, top, ro, ids, wts);
 }
 
 // logits given (32-bit [tokens, E]): ids and wts are chosen here first (see lsb_moe_route) and written
 LSB_API int lsb_moe_align(int* ids, float* wts, int n_tokens, int top, int E, int cap_tiles,
                           int tile, int* pos, int* row_token, float* row_scale, int* tile_expert,
-                          const float* logits, int score, int renorm, cudaStream_t stream) {
+                          const float* logits, int score, int renorm, const float* bias, float scale, float eps,
+                          cudaStream_t stream) {
+    const RouteOpts ro = {score, renorm, bias, scale, eps};
     if (n_tokens <= 0) return 0;
     const long long n = (long long)n_tokens * top;
     if (E <= 0 || E > 8192 || tile <= 0 || cap_tiles < (n + tile - 1) / tile + E) return (int)cudaErrorInvalidValue;
     if (logits && (top > kMaxTop || top > E || score < 0 || score > 1)) return (int)cudaErrorInvalidValue;
     return lsb_launch(moe_align_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, 1,
-                      ids, wts, (int)n, top, E, cap_tiles, tile, pos, row_token, row_scale, tile_expert, logits,
-                      score, renorm);
+                      ids, wts, (int)n, top, E, cap_tiles, tile, pos, row_token, row_scale, tile_expert, logits, ro);
 }
 
 // rows[pos[t, k]] = T(wts[t, k] * x[t]): the operand of the grouped tensor-core product, which wants
@@ -276,13 +297,13 @@ LSB_API int lsb_moe_gather(const void* x, int dtype, const int* pos, const float
 
 LSB_API int lsb_moe_up(const void* x, int dtype, const int* row_token, const float* row_scale, int on_input,
                        const void* w, const int* tile_expert, int cap_tiles, void* out, int F, int K,
-                       int act, cudaStream_t stream) {
+                       int act, float limit, cudaStream_t stream) {
     if (cap_tiles <= 0) return 0;
     if (F <= 0 || K <= 0 || cap_tiles > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((2 * F + kTile - 1) / kTile, cap_tiles);
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_gemm_kernel<T, 0>, grid, dim3(256), 0, stream, 1,
                                                 (const T*)x, row_token, row_scale, on_input, (const T*)w,
-                                                tile_expert, out, 2 * F, K, act));
+                                                tile_expert, out, 2 * F, K, act, limit));
     return 0;
 }
 
@@ -294,7 +315,7 @@ LSB_API int lsb_moe_down(const void* h, int dtype, const int* row_token, const v
     dim3 grid((N + kTile - 1) / kTile, cap_tiles);
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_gemm_kernel<T, 1>, grid, dim3(256), 0, stream, 1,
                                                 (const T*)h, row_token, (const float*)nullptr, 0, (const T*)w,
-                                                tile_expert, (void*)out, N, K, 0));
+                                                tile_expert, (void*)out, N, K, 0, 0.f));
     return 0;
 }
 

@@ -344,3 +344,147 @@ LSB_API int lsb_branch_mean(const void* const* ys, const float* const* ws, int n
     });
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same stream with centred norms that carry a weight and a bias (layer norm):
+//
+//     x <- x + mult * (cn(y) * w_post + b_post)        out = cn(x) * w_next + b_next
+//
+// with cn(z) = (z - mean z) / sqrt(mean((z - mean z)^2) + eps).  The mean is taken first and the
+// variance from the deviations (two passes over the row in shared memory), all in 32-bit.
+template <int V, typename T> struct RowIo;
+template <typename T> struct RowIo<1, T> {
+    static __device__ __forceinline__ void load(const T* p, float* v) { v[0] = lsb_to_float(p[0]); }
+    static __device__ __forceinline__ void store(T* p, const float* v) { p[0] = lsb_from_float<T>(v[0]); }
+};
+template <typename T> struct RowIo<4, T> {
+    static __device__ __forceinline__ void load(const T* p, float* v) {
+        const float4 x = row_load4(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(T* p, const float* v) { row_store4(p, make_float4(v[0], v[1], v[2], v[3])); }
+};
+
+// mean and 1 / sqrt(variance + eps) of the row in shared memory
+template <int V>
+__device__ __forceinline__ void centred_stats(const float* row_sh, int hidden, float sum, float eps, float* scratch,
+                                              float& mean, float& inv) {
+    mean = lsb_block_sum(sum, scratch) / (float)hidden;
+    float ss = 0.f;
+    for (int i = V * threadIdx.x; i < hidden; i += V * kRowThreads) {
+        float v[V];
+        RowIo<V, float>::load(row_sh + i, v);
+#pragma unroll
+        for (int u = 0; u < V; ++u) ss += (v[u] - mean) * (v[u] - mean);
+    }
+    inv = rsqrtf(lsb_block_sum(ss, scratch) / (float)hidden + eps);
+}
+
+template <typename T, bool GATHER, int V>
+__global__ void __launch_bounds__(kRowThreads)
+stream_centred_norm_kernel(float* __restrict__ residual, const T* __restrict__ y, const float* __restrict__ post_w,
+                           const float* __restrict__ post_b, float post_eps, float mult, const int* __restrict__ rows,
+                           const float* __restrict__ next_w, const float* __restrict__ next_b, float next_eps,
+                           T* __restrict__ out, int hidden, int n_rows_total) {
+    extern __shared__ float row_sh[];
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r_out = blockIdx.x;
+    int r_in = r_out;
+    if (GATHER) {
+        r_in = rows[r_out];
+        if (r_in < 0 || r_in >= n_rows_total) {
+            if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+            if (out)
+                for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)r_out * hidden + i] = lsb_from_float<T>(0.f);
+            return;
+        }
+    }
+    float* res = residual + (size_t)r_in * hidden;
+    const T* yr = y ? y + (size_t)r_in * hidden : nullptr;
+    float mean_y = 0.f, inv_y = 1.f;
+    if (yr && post_w) {
+        float s = 0.f;
+        for (int i = V * threadIdx.x; i < hidden; i += V * kRowThreads) {
+            float v[V];
+            RowIo<V, T>::load(yr + i, v);
+            RowIo<V, float>::store(row_sh + i, v);
+#pragma unroll
+            for (int u = 0; u < V; ++u) s += v[u];
+        }
+        centred_stats<V>(row_sh, hidden, s, post_eps, scratch, mean_y, inv_y);
+    }
+    float sum = 0.f;
+    for (int i = V * threadIdx.x; i < hidden; i += V * kRowThreads) {
+        float x[V];
+        RowIo<V, float>::load(res + i, x);
+        if (yr) {
+            float v[V];
+            if (post_w) {
+                float w[V], b[V];
+                RowIo<V, float>::load(row_sh + i, v);
+                RowIo<V, float>::load(post_w + i, w);
+                RowIo<V, float>::load(post_b + i, b);
+#pragma unroll
+                for (int u = 0; u < V; ++u) x[u] += mult * ((v[u] - mean_y) * inv_y * w[u] + b[u]);
+            } else {
+                RowIo<V, T>::load(yr + i, v);
+#pragma unroll
+                for (int u = 0; u < V; ++u) x[u] += mult * v[u];
+            }
+            if (!GATHER) RowIo<V, float>::store(res + i, x);
+        }
+        RowIo<V, float>::store(row_sh + i, x);
+#pragma unroll
+        for (int u = 0; u < V; ++u) sum += x[u];
+    }
+    if (!out) return;
+    float mean, inv;
+    centred_stats<V>(row_sh, hidden, sum, next_eps, scratch, mean, inv);
+    T* o = out + (size_t)r_out * hidden;
+    for (int i = V * threadIdx.x; i < hidden; i += V * kRowThreads) {
+        float x[V], w[V], b[V];
+        RowIo<V, float>::load(row_sh + i, x);
+        RowIo<V, float>::load(next_w + i, w);
+        RowIo<V, float>::load(next_b + i, b);
+#pragma unroll
+        for (int u = 0; u < V; ++u) x[u] = (x[u] - mean) * inv * w[u] + b[u];
+        RowIo<V, T>::store(o + i, x);
+    }
+}
+
+// y, (post_w, post_b) and (next_w, next_b, out) may each be null (post_w null with y given: a plain sum of
+// mult * y).  rows null: every row of the stream, in place; else the rows named, the stream untouched.
+LSB_API int lsb_stream_centred_norm(float* residual, const void* y, const float* post_w, const float* post_b,
+                                    float post_eps, float mult, const int* rows, int n_rows, const float* next_w,
+                                    const float* next_b, float next_eps, void* out, int dtype, int n_rows_total,
+                                    int hidden, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0 || (out && !(next_w && next_b)) || (post_w && !post_b)) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    bool vec = hidden % 4 == 0;
+    for (const void* ptr : {(const void*)residual, y, (const void*)post_w, (const void*)post_b, (const void*)next_w,
+                            (const void*)next_b, (const void*)out})
+        vec = vec && ((uintptr_t)ptr % 16 == 0);
+#define LSB_CENTRED_NORM(G, V)                                                                                     \
+    do {                                                                                                           \
+        if (smem > 48 * 1024) {                                                                                    \
+            int rc = (int)cudaFuncSetAttribute(stream_centred_norm_kernel<T, G, V>,                                \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+            if (rc) return rc;                                                                                     \
+        }                                                                                                          \
+        return lsb_launch(stream_centred_norm_kernel<T, G, V>, dim3(n_rows), dim3(kRowThreads), smem, stream, 1,   \
+                          residual, (const T*)y, post_w, post_b, post_eps, mult, rows, next_w, next_b, next_eps,   \
+                          (T*)out, hidden, n_rows_total);                                                          \
+    } while (0)
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (vec && rows) LSB_CENTRED_NORM(true, 4);
+        else if (vec) LSB_CENTRED_NORM(false, 4);
+        else if (rows) LSB_CENTRED_NORM(true, 1);
+        else LSB_CENTRED_NORM(false, 1);
+    });
+#undef LSB_CENTRED_NORM
+    return 0;
+}

@@ -245,6 +245,24 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: 
           _i(ids.shape[0]), _i(table.shape[1]), _i(table.shape[0]), _f(scale), _stream(out))
 
 
+def embedding_pair(table: torch.Tensor, pair_table: torch.Tensor, ctx, last_token: torch.Tensor, buckets: int,
+                   mul_prev: int, mul_cur: int, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = float(table[id_t, :]) * scale + float(pair_table[row_t, :]) with row_t = (id_(t-1) * mul_prev +
+    id_t * mul_cur) mod buckets, and row ``buckets`` for a sequence's first token.  ``last_token`` (int32, one
+    per request slot) holds the token before a portion's first and is left holding the portion's last."""
+    _req(table, "table", dim=2)
+    _req(pair_table, "pair_table", table.dtype, 2)
+    _req(last_token, "last_token", torch.int32, 1)
+    _req(out, "out", torch.float32, 2)
+    T = ctx.n_tokens
+    if out.shape != (T, table.shape[1]) or pair_table.shape != (buckets + 1, table.shape[1]):
+        raise KernelError("embedding_pair: out must be [tokens, hidden] and the pair table [buckets + 1, hidden]")
+    _call("embedding", "lsb_embedding_pair", _p(table), _p(pair_table), _i(_dt(table)), _p(ctx.token_ids),
+          _p(ctx.positions), _p(ctx.token_req), _p(ctx.q_start), _p(ctx.table_rows), _p(last_token), _p(out), _i(T),
+          _i(table.shape[1]), _i(table.shape[0]), _i(buckets), _ll(mul_prev), _ll(mul_cur), _i(last_token.shape[0]),
+          _f(scale), _stream(out))
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
                 eps: float, out: torch.Tensor) -> None:
     """residual += delta (in place, 32-bit); out = rmsnorm(residual) * weight."""
@@ -280,7 +298,10 @@ def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], ro
           _i(_dt(out)), _i(rows.shape[0]), _i(T), _i(H), _f(eps), _stream(out))
 
 
-ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3}     # act(gate) * up of a gated product
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3, "capped_glu": 5}     # act(gate) * up of a gated product
+# "capped_glu" has a limit L: min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1).  The products'
+# epilogues do not know it: such a product leaves gate and up side by side and the activation kernel follows.
+UNFUSED_GATED = ("capped_glu",)
 
 
 def _activation_id(name: str) -> int:
@@ -375,7 +396,7 @@ def finish_norm(x: NormOut) -> torch.Tensor:
 
 
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           gated: bool = False, activation: str = "silu", into=None):
+           gated: bool = False, activation: str = "silu", into=None, limit: float = 0.0):
     """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
 
     ``x`` may be a ``NormOut`` (the norm before this product, possibly half done: see there).
@@ -389,8 +410,15 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     ``gated``: the rows of ``w`` alternate gate_i, up_i and the result is [M, N / 2] with
     ``out[m, i] = act(d[m, 2i]) * d[m, 2i + 1]`` (applied in the product's epilogue on the
     tensor-core path, by the activation kernel otherwise); ``activation`` names act: "silu",
-    "gelu_tanh" or "none".
+    "gelu_tanh", "none", or "capped_glu" with its ``limit``.
     """
+    if gated and activation in UNFUSED_GATED:
+        if into is not None:
+            raise KernelError("linear: a product into the residual is plain and in the compute dtype")
+        raw = linear(x, w, out_dtype)
+        half = torch.empty((raw.shape[0], raw.shape[1] // 2), dtype=raw.dtype, device=raw.device)
+        gated_activation(raw, half, activation, limit)
+        return half
     act = _activation_id(activation) if gated else 0
     owed = None
     if isinstance(x, NormOut):
@@ -501,15 +529,18 @@ def tensor_core_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
-    """out[t, i] = act(gate_up[t, 2i]) * gate_up[t, 2i + 1] (gate and up alternate)."""
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> None:
+    """out[t, i] = act(gate_up[t, 2i]) * gate_up[t, 2i + 1] (gate and up alternate); "capped_glu" with ``limit`` L:
+    min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1)."""
+    if activation in UNFUSED_GATED and not limit > 0:
+        raise KernelError(f"gated_activation: '{activation}' needs a positive limit")
     _req(gate_up, "gate_up", dim=2)
     _req(out, "out", gate_up.dtype, 2)
     T, I = out.shape
     if gate_up.shape != (T, 2 * I):
         raise KernelError(f"gated_activation: gate_up is {tuple(gate_up.shape)}, out is {tuple(out.shape)}")
     _call("activation", "lsb_gated_act", _p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I),
-          _i(_activation_id(activation)), _stream(out))
+          _i(_activation_id(activation)), _f(limit), _stream(out))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -966,8 +997,8 @@ def latent_prep(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_w
         raise KernelError("latent_prep: cq, the weight or the step do not fit")
     if write:
         _req(kv_weight, "kv_weight", torch.float32, 1)
-        if ld != q_rank + kv_rank + rot_dim or kv_weight.shape[0] != kv_rank:
-            raise KernelError("latent_prep: down must hold q_rank + kv_rank + rot_dim columns")
+        if ld < q_rank + kv_rank + rot_dim or kv_weight.shape[0] != kv_rank:
+            raise KernelError("latent_prep: down must hold q_rank + kv_rank + rot_dim columns (more may follow)")
         if rot_dims:
             _req(inv_freq, "inv_freq", torch.float32, 1)
             if inv_freq.shape[0] != rot_dims // 2:
@@ -996,10 +1027,11 @@ def latent_query_rot(q: torch.Tensor, qf: torch.Tensor, heads: int, plain: int, 
           _i(rot_dims), _i(_PAIRINGS[pairing]), _p(inv_freq), _p(ctx.positions), _stream(qf))
 
 
-def batched_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+def batched_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, exact: bool = False) -> None:
     """out[m, h, :] = a[m, h, :] @ b[h].T for every h: ``a`` [M, H, K] and ``out`` [M, H, N] may be
     views with any row and head strides (unit stride along the last axis), ``b`` [H, N, K] is dense.
-    32-bit accumulation."""
+    32-bit accumulation.  ``exact``: 32-bit operands of ``a`` are not rounded on their way into the product
+    (the CUDA cores' multiply-add), whatever the dtype of ``b``."""
     for name, t in (("a", a), ("out", out)):
         _req(t, name, dim=3, contiguous=False)
         if t.stride(2) != 1:
@@ -1009,12 +1041,92 @@ def batched_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
     N = b.shape[1]
     if b.shape != (H, N, K) or out.shape != (M, H, N):
         raise KernelError(f"batched_nt: a {tuple(a.shape)}, b {tuple(b.shape)}, out {tuple(out.shape)} do not fit")
-    if LATENT_TENSOR_CORES and b.dtype == torch.bfloat16:
+    if LATENT_TENSOR_CORES and b.dtype == torch.bfloat16 and not exact:
         _call("latent_tc", "lsb_batched_nt_tc", _p(a), _i(_dt(a)), _ll(a.stride(0)), _ll(a.stride(1)), _p(b), _p(out),
               _i(_dt(out)), _ll(out.stride(0)), _ll(out.stride(1)), _i(M), _i(N), _i(K), _i(H), _stream(out))
         return
     _call("latent", "lsb_batched_nt", _p(a), _i(_dt(a)), _ll(a.stride(0)), _ll(a.stride(1)), _p(b), _i(_dt(b)),
           _p(out), _i(_dt(out)), _ll(out.stride(0)), _ll(out.stride(1)), _i(M), _i(N), _i(K), _i(H), _stream(out))
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; ``gate`` 32-bit [T, heads], rows may be strided."""
+    _req(x, "x", dim=3)
+    _req(gate, "gate", torch.float32, 2, contiguous=False)
+    T, H, D = x.shape
+    if gate.shape != (T, H) or gate.stride(1) != 1:
+        raise KernelError("head_gate: the gate must be [tokens, heads] with unit column stride")
+    _call("latent", "lsb_head_gate", _p(x), _i(_dt(x)), _p(gate), _ll(gate.stride(0)), _i(T), _i(H), _i(D), _stream(x))
+
+
+# ------------------------------------------------------- gated linear recurrent unit (real gates)
+def rglru_conv(proj: torch.Tensor, x_off: int, x_bias: Optional[torch.Tensor], taps_w: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], conv_state: torch.Tensor, ctx, u: torch.Tensor) -> None:
+    """u[t, c] = conv_bias[c] + sum_k taps_w[c, k] * xin[t - (taps - 1 - k), c] with xin = proj[:, x_off + c] +
+    x_bias[c]; before a portion's first token xin is the request slot's ``conv_state`` [slots, taps - 1, width]
+    (zeros before a sequence's start).  All 32-bit."""
+    _req(proj, "proj", torch.float32, 2)
+    _req(taps_w, "taps_w", torch.float32, 2)
+    _req(conv_state, "conv_state", torch.float32, 3)
+    _req(u, "u", torch.float32, 2)
+    T, width = u.shape
+    taps = taps_w.shape[1]
+    if ctx.n_tokens != T or proj.shape[0] != T or x_off < 0 or x_off + width > proj.shape[1] or taps_w.shape[0] != width \
+            or conv_state.shape[1] < taps - 1 or conv_state.shape[2] != width:
+        raise KernelError("rglru_conv: proj, the taps, the state and u disagree")
+    if taps > 1 and conv_state.shape[1] != taps - 1:
+        raise KernelError("rglru_conv: the state must hold taps - 1 inputs")
+    for name, t in (("x_bias", x_bias), ("conv_bias", conv_bias)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != width:
+                raise KernelError(f"rglru_conv: {name} must have {width} entries")
+    _call("rglru", "lsb_rglru_conv", _p(proj), _ll(proj.stride(0)), _i(x_off), _p(x_bias), _p(taps_w), _p(conv_bias),
+          _i(taps), _p(conv_state), _p(ctx.token_req), _p(ctx.q_start), _p(ctx.table_rows), _i(conv_state.shape[0]),
+          _p(u), _i(width), _i(T), _stream(u))
+
+
+def rglru_gates(gates: torch.Tensor, r_bias: Optional[torch.Tensor], i_bias: Optional[torch.Tensor],
+                lam: torch.Tensor, rate: float, u: torch.Tensor, proj: torch.Tensor, y_off: int,
+                y_bias: Optional[torch.Tensor], blocks: int) -> None:
+    """In place, 32-bit: with channel c = b * bw + o, ``gates[t, b, o]`` (the decay gate's product) becomes
+    a = exp(-rate * sigmoid(. + r_bias) * softplus(lam)), ``gates[t, b, bw + o]`` (the input gate's product) becomes
+    sqrt(1 - a^2) * sigmoid(. + i_bias) * u, and ``proj[t, y_off + c]`` becomes gelu_tanh(. + y_bias)."""
+    _req(gates, "gates", torch.float32, 2)
+    _req(u, "u", torch.float32, 2)
+    _req(proj, "proj", torch.float32, 2)
+    _req(lam, "lam", torch.float32, 1)
+    T, width = u.shape
+    if gates.shape != (T, 2 * width) or proj.shape[0] != T or y_off < 0 or y_off + width > proj.shape[1] \
+            or lam.shape[0] != width or blocks <= 0 or width % blocks:
+        raise KernelError("rglru_gates: gates, u, proj and the decay's parameter disagree")
+    for name, t in (("r_bias", r_bias), ("i_bias", i_bias), ("y_bias", y_bias)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != width:
+                raise KernelError(f"rglru_gates: {name} must have {width} entries")
+    _call("rglru", "lsb_rglru_gates", _p(gates), _p(r_bias), _p(i_bias), _p(lam), _f(rate), _p(u), _p(proj),
+          _ll(proj.stride(0)), _i(y_off), _p(y_bias), _i(width), _i(blocks), _i(T), _stream(u))
+
+
+def rglru_walk(gates: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, x_bias: Optional[torch.Tensor],
+               taps: int, state: torch.Tensor, conv_state: torch.Tensor, ctx, out: torch.Tensor, blocks: int) -> None:
+    """S <- a_t S + in_t token by token for every request and channel, from the slot's ``state`` [slots, width] and
+    back into it; out[t] = S_t * proj[t, y_off:] in the compute dtype.  ``gates`` as ``rglru_gates`` left them.  The
+    slot's ``conv_state`` is left holding the x branch's last ``taps - 1`` inputs."""
+    _req(gates, "gates", torch.float32, 2)
+    _req(proj, "proj", torch.float32, 2)
+    _req(state, "state", torch.float32, 2)
+    _req(conv_state, "conv_state", torch.float32, 3)
+    _req(out, "out", dim=2)
+    T, width = out.shape
+    if gates.shape != (T, 2 * width) or proj.shape[0] != T or ctx.n_tokens != T or state.shape[1] != width \
+            or conv_state.shape[0] != state.shape[0] or conv_state.shape[2] != width \
+            or (taps > 1 and conv_state.shape[1] != taps - 1) or max(x_off, y_off) + width > proj.shape[1]:
+        raise KernelError("rglru_walk: gates, proj, the states and out disagree")
+    _call("rglru", "lsb_rglru_walk", _p(gates), _p(proj), _ll(proj.stride(0)), _i(x_off), _i(y_off), _p(x_bias),
+          _i(taps), _p(state), _p(conv_state), _p(ctx.q_start), _p(ctx.table_rows), _i(state.shape[0]), _p(out),
+          _i(_dt(out)), _i(width), _i(blocks), _i(ctx.n_requests), _stream(out))
 
 
 def latent_attention(qf: torch.Tensor, ctx, cache, kv_rank: int, rot_dim: int, scale: float,
@@ -1085,6 +1197,43 @@ def stream_norm(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: 
           _i(T), _i(H), _stream(residual))
 
 
+def stream_centred_norm(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
+                        post_bias: Optional[torch.Tensor], post_eps: float, mult: float, rows: Optional[torch.Tensor],
+                        next_weight: Optional[torch.Tensor], next_bias: Optional[torch.Tensor], next_eps: float,
+                        out: Optional[torch.Tensor]) -> None:
+    """residual += mult * (cn(y) * post_weight + post_bias); out = cn(residual) * next_weight + next_bias, with
+    cn(z) = (z - mean z) / sqrt(mean((z - mean z)^2) + eps).  Every piece is optional (``post_weight`` None with
+    ``y`` given: a plain sum of mult * y).  ``rows`` (int32): only those rows, into ``out`` [len(rows), H], the
+    stream untouched."""
+    _req(residual, "residual", torch.float32, 2)
+    T, H = residual.shape
+    n = T if rows is None else rows.shape[0]
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+    dtype = None
+    for name, t in (("y", y), ("out", out)):
+        if t is not None:
+            _req(t, name, dtype, 2)
+            dtype = t.dtype
+    if dtype is None:
+        return
+    if y is not None and y.shape != (T, H):
+        raise KernelError("stream_centred_norm: y has another shape than the stream")
+    if out is not None and (out.shape != (n, H) or next_weight is None or next_bias is None):
+        raise KernelError("stream_centred_norm: out must be [rows, H] and needs the weight and bias of its norm")
+    if (post_weight is None) != (post_bias is None):
+        raise KernelError("stream_centred_norm: the norm behind the sublayer needs weight and bias")
+    for name, t in (("post_weight", post_weight), ("post_bias", post_bias), ("next_weight", next_weight),
+                    ("next_bias", next_bias)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != H:
+                raise KernelError(f"stream_centred_norm: {name} must have {H} entries")
+    _call("sandwich", "lsb_stream_centred_norm", _p(residual), _p(y), _p(post_weight), _p(post_bias), _f(post_eps),
+          _f(mult), _p(rows), _i(n), _p(next_weight), _p(next_bias), _f(next_eps), _p(out),
+          _i(_F32 if dtype == torch.float32 else _BF16), _i(T), _i(H), _stream(residual))
+
+
 def branch_mean(ys, weights, eps: float, out: torch.Tensor) -> None:
     """out = mean over the branches b of unit(ys[b]) * weights[b], row by row."""
     _req(out, "out", dim=2)
@@ -1115,13 +1264,17 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
                    ctx, cache, q_out: torch.Tensor, *, q_bias=None, k_bias=None, v_bias=None, q_norm=None,
                    k_norm=None, norm_eps: float = 0.0, temp_coef: float = 0.0, temp_every: int = 0,
                    inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, pairing: str = "half",
-                   store: bool = True, norm_all: bool = False, v_unit: bool = False) -> None:
+                   store: bool = True, norm_all: bool = False, v_unit: bool = False,
+                   v_first: Optional[torch.Tensor] = None, v_lambda: Optional[torch.Tensor] = None) -> None:
     """From the rows of ``proj`` (q at ``q_off``, k at ``k_off``, v at ``v_off``) to queries in ``q_out``
     [T, nh * dk] and keys and values in this step's cache places: biases, a norm per head of q and k
     (one weight of head size each), the query temperature ``1 + coef * ln(floor((pos + 1) / every) + 1)``
     and the rotation of the first ``rotary_dim`` dims, each if given.  ``norm_all``: q and k are each
     normed over all their heads at once, with weights as long as the whole projection.  ``v_unit``: every
-    value head is divided by its root mean square (eps ``norm_eps``, no weight) on its way into the cache."""
+    value head is divided by its root mean square (eps ``norm_eps``, no weight) on its way into the cache.
+    ``v_first`` [T, nkv * dv] (rows may be strided) with ``v_lambda`` (one 32-bit number on the device): the
+    values are mixed with those another layer made of the same tokens, v <- (1 - lambda) v + lambda v_first,
+    and cached so."""
     _req(proj, "proj", dim=2)
     _req(q_out, "q_out", proj.dtype, 2)
     T, ld = proj.shape
@@ -1145,13 +1298,20 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
                               "frequencies")
     if norm_all and (q_norm is None) != (k_norm is None):
         raise KernelError("attention_prep: a norm over all heads needs both weights")
+    v_first_ld = 0
+    if v_first is not None:
+        _req(v_first, "v_first", proj.dtype, 2, contiguous=False)
+        _req(v_lambda, "v_lambda", torch.float32)
+        if v_first.shape != (T, nkv * dv) or v_first.stride(1) != 1 or v_lambda.numel() != 1 or v_unit:
+            raise KernelError("attention_prep: v_first must be [T, kv heads * value size] with one mixing number")
+        v_first_ld = v_first.stride(0)
     _check_kv_cache(cache, nkv, dk, dv, proj.dtype)
     _call("attention_prep", "lsb_attention_prep", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
           _i(T), _i(nh), _i(nkv), _i(dk), _i(dv), _p(q_bias), _p(k_bias), _p(v_bias), _p(q_norm), _p(k_norm),
           _f(norm_eps), _i(1 if norm_all else 0), _i(1 if v_unit else 0), _f(temp_coef), _i(temp_every), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
           _i(_PAIRINGS[pairing]), _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows), _p(cache.block_table),
           _i(cache.block_table.shape[1]), _p(q_out), _p(cache.k_pages), _p(cache.v_pages), _i(cache.page_size),
-          _i(cache.k_pages.shape[0]), _i(1 if store else 0), _stream(proj))
+          _i(cache.k_pages.shape[0]), _i(1 if store else 0), _p(v_first), _ll(v_first_ld), _p(v_lambda), _stream(proj))
 
 
 DV_BLOCK_SHAPE = 0              # 0: by the grid's size; 1: 64-row blocks; 2, 3: 16-row blocks, two or four tiles in flight; 4: as 3, keys shared by three blocks
@@ -1160,13 +1320,14 @@ DV_TENSOR_CORES = True          # bfloat16 heads of multiples of 16 up to 128 on
 
 def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cache, scale: float, window: int,
                  chunk: int, gate: Optional[torch.Tensor], out: torch.Tensor, sink: bool = False,
-                 gate_per_head: bool = False) -> None:
+                 gate_per_head: bool = False, softcap: float = 0.0, linear_bias: bool = False) -> None:
     """Softmax attention of this step's queries ``q`` [T, nh * dk] over their requests' cached keys (size
     dk) and values (size dv): a query at position p sees ``[lo, p]`` with lo the larger of
     ``p - window + 1`` (window > 0) and the start of p's chunk of ``chunk`` positions (chunk > 0).
     ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate); with ``gate_per_head`` it is
     [T, nh], one number per head.  ``sink``: one is added to the softmax's denominator (a place with
-    score 0 and no value).
+    score 0 and no value).  ``softcap`` > 0: a scaled score s becomes softcap * tanh(s / softcap).
+    ``linear_bias``: head h's score for the key at distance d loses 2^(-8 (h + 1) / nh) * d (after the cap).
 
     bfloat16 with both sizes multiples of 16 up to 128 runs on the tensor cores (prompt portions in
     tiles of 64 rows, a row being a position and a head of a kv head's group; single tokens with the
@@ -1186,14 +1347,17 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
         if gate.shape != (T, nh if gate_per_head else nh * dv) or gate.stride(1) != 1:
             raise KernelError("attention_dv: the gate must be [T, heads * value size] (or [T, heads]) with unit column stride")
         gate_stride = gate.stride(0)
-    flags = (1 if sink else 0) | (2 if gate is not None and gate_per_head else 0)
+    flags = (1 if sink else 0) | (2 if gate is not None and gate_per_head else 0) | (4 if linear_bias else 0)
+    softcap = float(softcap or 0.0)
+    if softcap < 0:
+        raise KernelError("attention_dv: the cap must be positive (0: none)")
     _check_kv_cache(cache, nkv, dk, dv, q.dtype)
     # equal key and value sizes, no chunks, no gate or one number a head: the prompt portions of a step go
     # to the tcgen05 prompt kernel, which takes the sink and that gate in its last step; single tokens,
     # where they all come before the portions (as the scheduler puts them), go on below
     n_req, max_q = ctx.n_requests, ctx.max_q_len
     if (USE_TCGEN05_ATTENTION and DV_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
-            and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128
+            and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128 and not softcap and not linear_bias
             and cache.page_size in (8, 16, 32, 64)
             and _lib("attention_tc5").lsb_prefill_attention_tc5_supported(
                 _p(q), _i(q.shape[1]), _p(cache.k_pages), _p(cache.v_pages), _i(nh), _i(nkv), _i(dk), _i(cache.page_size))):
@@ -1228,12 +1392,13 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
               _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
               _ll(gate_stride), _p(out), _i(n_req), _i(max_q), _i(nh), _i(nkv), _i(dk), _i(dv),
               _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(num_sms(q.device)),
-              _i(DV_BLOCK_SHAPE), _p(scratch), _i(flags), _stream(out))
+              _i(DV_BLOCK_SHAPE), _p(scratch), _i(flags), _f(softcap), _stream(out))
         return
     _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
           _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
           _ll(gate_stride), _p(out), _i(_dt(q)), _i(n_req), _i(max_q), _i(nh), _i(nkv), _i(dk),
-          _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(flags), _stream(out))
+          _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(flags), _f(softcap),
+          _stream(out))
 
 
 def branch_sum(ys, scales, out: torch.Tensor) -> None:
@@ -1493,9 +1658,20 @@ def moe_tile() -> int:
     return int(_lib("moe").lsb_moe_tile())
 
 
+def _route_options(E: int, choice_bias: Optional[torch.Tensor], weight_scale: float, renorm_eps: float):
+    if choice_bias is not None:
+        _req(choice_bias, "choice_bias", torch.float32, 1)
+        if choice_bias.shape[0] != E:
+            raise KernelError(f"moe: the choice bias must have {E} entries")
+    return _p(choice_bias), _f(weight_scale), _f(renorm_eps)
+
+
 def moe_route(logits: torch.Tensor, top: int, score: str, renormalize: bool, ids: torch.Tensor,
-              weights: torch.Tensor) -> None:
-    """The ``top`` experts with the largest scores per row of 32-bit ``logits`` and their scores."""
+              weights: torch.Tensor, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
+              renorm_eps: float = 0.0) -> None:
+    """The ``top`` experts with the largest scores per row of 32-bit ``logits`` and their scores.
+    ``choice_bias`` (one number an expert) is added to the scores for the choice only; the weights are the
+    chosen scores themselves, divided by their sum + ``renorm_eps`` if ``renormalize``, times ``weight_scale``."""
     _req(logits, "logits", torch.float32, 2)
     _req(ids, "ids", torch.int32, 2)
     _req(weights, "weights", torch.float32, 2)
@@ -1503,7 +1679,8 @@ def moe_route(logits: torch.Tensor, top: int, score: str, renormalize: bool, ids
     if ids.shape != (T, top) or weights.shape != (T, top) or not 0 < top <= min(E, 32):
         raise KernelError("moe_route: ids / weights must be [tokens, top], top at most 32")
     _call("moe", "lsb_moe_route", _p(logits), _i(T), _i(E), _i(top), _i(MOE_SCORES[score]),
-          _i(1 if renormalize else 0), _p(ids), _p(weights), _stream(ids))
+          _i(1 if renormalize else 0), *_route_options(E, choice_bias, weight_scale, renorm_eps), _p(ids), _p(weights),
+          _stream(ids))
 
 
 MOE_FUSED_ROUTING_TOKENS = 256  # steps of at most this many tokens choose their experts inside the sorting kernel
@@ -1511,7 +1688,8 @@ MOE_FUSED_ROUTING_TOKENS = 256  # steps of at most this many tokens choose their
 
 def moe_routed_experts(x: torch.Tensor, logits: torch.Tensor, top: int, score: str, renormalize: bool,
                        w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str, weight_on: str,
-                       out: torch.Tensor) -> None:
+                       out: torch.Tensor, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
+                       renorm_eps: float = 0.0, limit: float = 0.0) -> None:
     """``moe_route`` on the 32-bit ``logits`` followed by ``moe_experts``; in a step of few tokens the
     choosing rides in the kernel that sorts the rows by expert (one launch less)."""
     _req(logits, "logits", torch.float32, 2)
@@ -1522,14 +1700,16 @@ def moe_routed_experts(x: torch.Tensor, logits: torch.Tensor, top: int, score: s
         raise KernelError("moe_routed_experts: top must be in [1, min(experts, 32)]")
     if T <= MOE_FUSED_ROUTING_TOKENS:
         moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out,
-                    route=(logits, MOE_SCORES[score], 1 if renormalize else 0))
+                    route=(logits, MOE_SCORES[score], 1 if renormalize else 0, choice_bias, weight_scale, renorm_eps),
+                    limit=limit)
     else:
-        moe_route(logits, top, score, renormalize, ids, weights)
-        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out)
+        moe_route(logits, top, score, renormalize, ids, weights, choice_bias, weight_scale, renorm_eps)
+        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out, limit=limit)
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor, route=None) -> None:
+                w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor, route=None,
+                limit: float = 0.0) -> None:
     """out[t] = sum over k of down_e(act(gate_e u) * up_e u), e = ids[t, k], with u = weights[t, k] * x[t]
     (``weight_on`` "input") or u = x[t] and the sum weighted ("output").  ``w_gate_up`` [E, 2F, H] has
     rows alternating gate_i, up_i; ``w_down`` [E, H, F]."""
@@ -1559,23 +1739,36 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     y = torch.empty(cap_tiles * tile, H, dtype=x.dtype if tc else torch.float32, device=dev)
     s = _stream(out)
     on_input = 1 if weight_on == "input" else 0
-    r_logits, r_score, r_renorm = route if route is not None else (None, 0, 0)
+    r_logits, r_score, r_renorm, r_bias, r_scale, r_eps = (tuple(route) + (None, 1.0, 0.0))[:6] if route is not None \
+        else (None, 0, 0, None, 1.0, 0.0)
     if r_logits is not None and r_logits.shape != (T, E):
         raise KernelError("moe_experts: the router's logits must be [tokens, experts]")
+    unfused = activation in UNFUSED_GATED
+    if unfused and not limit > 0:
+        raise KernelError(f"moe_experts: '{activation}' needs a positive limit")
     _call("moe", "lsb_moe_align", _p(ids), _p(weights), _i(T), _i(top), _i(E), _i(cap_tiles), _i(tile), _p(pos),
-          _p(row_token), _p(row_scale), _p(tile_expert), _p(r_logits), _i(r_score), _i(r_renorm), s)
+          _p(row_token), _p(row_scale), _p(tile_expert), _p(r_logits), _i(r_score), _i(r_renorm),
+          *_route_options(E, r_bias, r_scale, r_eps), s)
     if tc:
         rows = torch.empty(cap_tiles * tile, H, dtype=x.dtype, device=dev)
         _call("moe", "lsb_moe_gather", _p(x), _i(_dt(x)), _p(pos), _p(weights), _i(on_input), _i(T), _i(top),
               _i(cap_tiles * tile), _i(H), _p(rows), s)
         _chain_ends()
-        _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),
-              _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(_activation_id(activation)), s)
+        if unfused:
+            # (gate and up leave the product side by side; rows of unused tiles hold whatever the buffer held,
+            # and nothing reads what becomes of them)
+            raw = torch.empty(cap_tiles * tile, 2 * F, dtype=x.dtype, device=dev)
+            _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(raw), _i(0), _i(cap_tiles * tile),
+                  _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(0), s)
+            gated_activation(raw, hidden, activation, limit)
+        else:
+            _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),
+                  _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(_activation_id(activation)), s)
         _call("gemm_tc", "lsb_gemm_tc_grouped", _p(hidden), _p(w_down), _p(y), _i(0), _i(cap_tiles * tile),
               _i(H), _i(F), _i(E), _p(tile_expert), _i(0), s)
     else:
         _call("moe", "lsb_moe_up", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input), _p(w_gate_up),
-              _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), s)
+              _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), _f(limit), s)
         _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
               _p(y), _i(H), _i(F), s)
     _call("moe", "lsb_moe_combine", _p(y), _i(1 if tc else 0), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top),

@@ -50,6 +50,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "attention_dv": "attention_dv.cu",
     "matrix_memory": "matrix_memory.cu",
     "delta_rule": "delta_rule.cu",
+    "rglru": "rglru.cu",
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler

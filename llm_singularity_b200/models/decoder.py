@@ -97,6 +97,9 @@ class DecoderModel:
     def cache_specs(self) -> List[object]:
         """What each cache id of the run order must hold (from the mixer that writes it)."""
         specs: List[object] = [None] * self.spec.num_caches
+        own = self.embedding.cache_spec()
+        if own is not None:                     # what the embedding keeps per request: one more cache id
+            specs.append(own)
         for call in self.spec.order:
             cs = self.blocks[call.block].mixer.cache_spec()
             if call.writes_cache or specs[call.cache] is None:
@@ -163,7 +166,10 @@ class DecoderModel:
         meets first, the next block's, and may fold it into its last product; such steps are not
         recorded."""
         ops = self.rt.ops
-        residual = self.embedding.forward(ctx.token_ids)
+        if self.embedding.cache_spec() is not None:      # (its cache id follows the run order's)
+            residual = self.embedding.forward(ctx.token_ids, ctx, caches.view(self.spec.num_caches, ctx))
+        else:
+            residual = self.embedding.forward(ctx.token_ids)
         fold = getattr(ops, "folds_norm", None)
         fold = fold is not None and fold(residual.shape[0], self.rt.dtype)
         replay = getattr(ops, "LAYER_REPLAY", False) and hasattr(ops, "LayerRecording") and not fold

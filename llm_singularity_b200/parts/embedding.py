@@ -17,7 +17,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import NORMS, ParamSpec, Part
+from .base import NORMS, ParamSpec, Part, StateSpec
 
 
 class Embedding(Part):
@@ -30,17 +30,33 @@ class Embedding(Part):
         if getattr(spec, "side_size", 0):
             # a second table of per-token inputs that blocks pick their columns from
             p["side_weight"] = ParamSpec((spec.vocab_size, spec.side_size), role="table")
+        if getattr(spec, "pair_buckets", 0):
+            # a table indexed by a hash of the token and the one before it, added to the token's row
+            p["pair_weight"] = ParamSpec((spec.pair_buckets + 1, spec.hidden_size), role="table")
         return p
 
     def load(self, tensors):
         self.weight = tensors["weight"].contiguous()
         if "side_weight" in tensors:
             self.side_weight = tensors["side_weight"].contiguous()
+        if "pair_weight" in tensors:
+            self.pair_weight = tensors["pair_weight"].contiguous()
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def cache_spec(self):
+        """What the embedding keeps per request between steps: with a table of token pairs, the last
+        token of the step before (one int per slot); else nothing."""
+        return StateSpec((), dtype=torch.int32) if getattr(self.spec, "pair_buckets", 0) else None
+
+    def forward(self, token_ids: torch.Tensor, ctx=None, cache=None) -> torch.Tensor:
         out = self.rt.empty(token_ids.shape[0], self.spec.hidden_size, dtype=torch.float32)
         scale = float(getattr(self.spec, "scale", 1.0))
-        if scale != 1.0:
+        if getattr(self.spec, "pair_buckets", 0):
+            if ctx is None or cache is None:
+                raise ValueError("an embedding with a table of token pairs needs the step and its state")
+            s = self.spec
+            self.rt.ops.embedding_pair(self.weight, self.pair_weight, ctx, cache.state, s.pair_buckets, s.pair_mul_prev,
+                                       s.pair_mul_cur, out, scale)
+        elif scale != 1.0:
             self.rt.ops.embedding(self.weight, token_ids, out, scale)
         else:
             self.rt.ops.embedding(self.weight, token_ids, out)

@@ -10,7 +10,11 @@ temperature, rotation, window, chunk and gate is there only if the spec asks for
 softmax, norms, positions and angles are 32-bit.  Further options of the spec: the norm of q and k
 taken over all heads at once (``qk_norm_span`` "all"), value heads brought to unit rms before they
 are cached (``v_unit_norm``), one more place with score 0 and no value in every softmax (``sink``),
-and a gate of one number per head (``gate_per_head``).
+and a gate of one number per head (``gate_per_head``); scores capped by ``cap * tanh(s / cap)``
+(``logit_softcap``) and lowered in proportion to the key's distance with a slope per head
+(``linear_bias``); and values shared within a token among the layers of a model that name the same
+``value_mix_key``: the "source" layer lends the rows of its value projection to the step
+(``ctx.lent``), a "mixed" layer caches ``(1 - lambda) v + lambda v_source``.
 
 Where the spec is what the framework's grouped attention already covers after the preparation (keys
 and values of one size, no chunks, no gate), the same attention kernels run (tensor cores for
@@ -46,6 +50,13 @@ class KVAttention(Part):
         self.v_unit = bool(getattr(s, "v_unit_norm", False))
         self.sink = bool(getattr(s, "sink", False))
         self.gate_per_head = bool(getattr(s, "gate_per_head", False))
+        self.softcap = float(getattr(s, "logit_softcap", None) or 0.0)
+        self.linear_bias = bool(getattr(s, "linear_bias", False))
+        self.value_mix = getattr(s, "value_mix", None)
+        if self.value_mix not in (None, "source", "mixed"):
+            raise ValueError(f"value_mix '{self.value_mix}' is not known (source, mixed)")
+        if self.value_mix and (s.qkv_bias or self.v_unit):
+            raise ValueError("values that layers share are neither biased nor normed")
         self.position = POSITIONS.build(s.position, rt)
         self.table = self.position.rotary_table()
         if self.table is None and s.position.kind != "none":
@@ -57,7 +68,7 @@ class KVAttention(Part):
         self.o_size = s.num_heads * s.value_dim
         # the framework's grouped attention takes over where nothing here is beyond it
         self.plain = (s.key_dim == s.value_dim and s.chunk is None and not s.out_gate and s.key_dim % 16 == 0
-                      and 16 <= s.key_dim <= 256 and not self.sink)
+                      and 16 <= s.key_dim <= 256 and not self.sink and not self.softcap and not self.linear_bias)
         if self.plain:
             self.kernels = self.kernels + ("attention",)
             if rt.dtype == torch.bfloat16 and s.key_dim in (64, 128):
@@ -83,6 +94,8 @@ class KVAttention(Part):
                      k_norm=ParamSpec((k if whole else s.key_dim,), role="vector", init="ones"))
         if s.out_gate:
             p["g"] = ParamSpec((s.num_heads if getattr(s, "gate_per_head", False) else o, H))
+        if getattr(s, "value_mix", None) == "mixed":
+            p["vmix"] = ParamSpec((), role="vector", init="normal")
         return p
 
     def children(self):
@@ -94,6 +107,7 @@ class KVAttention(Part):
         self.w_out = tensors["o"].contiguous()
         self.extras = {n: tensors[n].contiguous() for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")
                        if n in tensors}
+        self.v_lambda = tensors["vmix"].reshape(1).contiguous() if "vmix" in tensors else None
 
     def cache_spec(self):
         s = self.spec
@@ -105,10 +119,19 @@ class KVAttention(Part):
         proj = ops.linear(x, self.w_in)                                   # [T, q | k | v | g]
         q = self.rt.empty(T, self.q_size)
         inv_freq, rotary_dim = self.table if self.table is not None else (None, 0)
+        v_off = self.q_size + self.k_size
+        if self.value_mix:
+            # what the layers of a step lend one another lives with the step: here the rows of the
+            # source layer's value projection (the tensor stays alive as long as the step does)
+            lent = ctx.__dict__.setdefault("lent", {})
+            if self.value_mix == "source":
+                lent[s.value_mix_key] = proj[:, v_off:v_off + self.v_size]
+            elif s.value_mix_key not in lent:
+                raise ValueError(f"no layer before this one lent '{s.value_mix_key}' to the step")
         ops.attention_prep(proj, 0, self.q_size, self.q_size + self.k_size, s.num_heads, s.num_kv_heads,
                            s.key_dim, s.value_dim, ctx, cache, q, norm_eps=s.eps, temp_coef=s.temp_coef,
                            temp_every=s.temp_every, inv_freq=inv_freq, rotary_dim=rotary_dim, pairing=self.pairing,
-                           store=writes_cache, **self.extras, **self._prep_options())
+                           store=writes_cache, **self.extras, **self._prep_options(ctx))
         out = self.rt.empty(T, self.o_size)
         if self.plain:
             ops.paged_attention(q, s.num_heads, s.num_kv_heads, s.key_dim, ctx, cache, s.scale, s.window or 0, out)
@@ -118,9 +141,11 @@ class KVAttention(Part):
                              s.window or 0, s.chunk or 0, gate, out, **self._softmax_options())
         return ops.linear(out, self.w_out)
 
-    def _prep_options(self) -> dict:
+    def _prep_options(self, ctx=None) -> dict:
         """Keyword arguments of the preparation kernel that only some specs need."""
         opts = {}
+        if self.value_mix == "mixed":
+            opts.update(v_first=ctx.lent[self.spec.value_mix_key], v_lambda=self.v_lambda)
         if self.norm_all:
             opts["norm_all"] = True
         if self.v_unit:
@@ -133,4 +158,8 @@ class KVAttention(Part):
             opts["sink"] = True
         if self.gate_per_head and self.spec.out_gate:
             opts["gate_per_head"] = True
+        if self.softcap:
+            opts["softcap"] = self.softcap
+        if self.linear_bias:
+            opts["linear_bias"] = True
         return opts

@@ -11,7 +11,8 @@ query is carried into the latent's space once per step (a product per head), att
 the cache rows themselves (every head reads the same rows, whose first ``kv_rank`` values are
 also the values), and ``W_uv[h]`` is applied to the weighted sum of latents afterwards.  A layer
 with ``reads_only`` has no W_dkv and attends over the rows another layer's call wrote in the same
-step (the run order names that cache).  Norms, angles, scores, softmax and weighted sums are
+step (the run order names that cache).  ``gate_per_head``: W_g (one row a head) rides in the same
+product as the down projections and ``sigmoid(W_g x)_h`` multiplies head h's output.  Norms, angles, scores, softmax and weighted sums are
 32-bit.
 """
 from __future__ import annotations
@@ -53,6 +54,8 @@ class LatentAttention(Part):
              "uk": ParamSpec((s.num_heads * s.plain_dim, s.kv_rank)),
              "uv": ParamSpec((s.num_heads * s.value_dim, s.kv_rank)),
              "o": ParamSpec((H, s.num_heads * s.value_dim))}
+        if getattr(s, "gate_per_head", False):
+            p["g"] = ParamSpec((s.num_heads, H))
         if not s.reads_only:
             p["dkv"] = ParamSpec((s.kv_rank + s.rot_dim, H))
             p["dkv_norm"] = ParamSpec((s.kv_rank,), role="vector", init="ones")
@@ -64,7 +67,9 @@ class LatentAttention(Part):
     def load(self, tensors):
         s = self.spec
         # one product for both down projections: rows of W_dq, then W_dkv
-        self.w_down = (tensors["dq"] if s.reads_only else torch.cat([tensors["dq"], tensors["dkv"]], dim=0)).contiguous()
+        rows = [tensors["dq"]] + ([] if s.reads_only else [tensors["dkv"]]) + ([tensors["g"]] if "g" in tensors else [])
+        self.w_down = torch.cat(rows, dim=0).contiguous()
+        self.gate_off = self.w_down.shape[0] - s.num_heads if "g" in tensors else None
         self.q_norm = tensors["dq_norm"]
         self.kv_norm = tensors.get("dkv_norm")
         self.w_uq = tensors["uq"].contiguous()
@@ -95,4 +100,6 @@ class LatentAttention(Part):
         ops.latent_attention(qf, ctx, cache, s.kv_rank, s.rot_dim, s.scale, mixed)
         heads_out = self.rt.empty(T, s.num_heads, s.value_dim)
         ops.batched_nt(mixed, self.w_uv, heads_out)
+        if self.gate_off is not None:
+            ops.head_gate(heads_out, down[:, self.gate_off:self.gate_off + s.num_heads])
         return ops.linear(heads_out.view(T, s.num_heads * s.value_dim), self.w_out)

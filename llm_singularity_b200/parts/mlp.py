@@ -87,7 +87,11 @@ class GatedMLP(Part):
 
     def forward(self, x, ctx, into=None):
         ops = self.rt.ops
-        act = ops.linear(x, self.w_gate_up, gated=True, activation=self.spec.activation)   # [T, I]
+        limit = float(getattr(self.spec, "limit", 0.0))
+        if limit:
+            act = ops.linear(x, self.w_gate_up, gated=True, activation=self.spec.activation, limit=limit)
+        else:
+            act = ops.linear(x, self.w_gate_up, gated=True, activation=self.spec.activation)   # [T, I]
         if into is not None:
             return ops.linear(act, self.w_down, into=into)
         return ops.linear(act, self.w_down)

@@ -94,6 +94,59 @@ class RMSNorm(Part):
         return out
 
 
+class CentredDelta:
+    """A sublayer's output that a centred norm with weight and bias behind the sublayer still has to take
+    before it joins the stream: ``stream += mult * (centred(values) * weight + bias)``."""
+
+    __slots__ = ("values", "weight", "bias", "eps", "mult")
+
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, mult: float):
+        self.values, self.weight, self.bias, self.eps, self.mult = values, weight, bias, float(eps), float(mult)
+
+
+@register_norm("layernorm")
+class LayerNorm(Part):
+    """``(x - mean) / sqrt(var + eps) * w + b`` over the model width, all in 32-bit, fused with the sum
+    into the stream that precedes it and, where a norm of this kind stands behind the sublayer whose
+    output is summed (``pending``), with that norm too."""
+
+    graph_safe = True
+    replayable = True
+    kernels = ("sandwich",)
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((spec.size,), role="vector", init="ones"),
+                "bias": ParamSpec((spec.size,), role="vector", init="normal")}
+
+    def load(self, tensors):
+        self.weight, self.bias = tensors["weight"].contiguous(), tensors["bias"].contiguous()
+
+    def pending(self, values: torch.Tensor, mult: float = 1.0) -> CentredDelta:
+        """``values`` as something this norm takes before it is added to the stream ``mult`` times."""
+        return CentredDelta(values, self.weight, self.bias, self.spec.eps, mult)
+
+    def _run(self, residual, delta, rows):
+        y = w = b = None
+        eps, mult = 0.0, 1.0
+        if isinstance(delta, CentredDelta):
+            y, w, b, eps, mult = delta.values, delta.weight, delta.bias, delta.eps, delta.mult
+        elif isinstance(delta, torch.Tensor):
+            y = delta
+        elif delta is not None and not isinstance(delta, StreamCopy):
+            raise ValueError(f"a centred norm cannot take a pending {type(delta).__name__}")
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.empty(n, residual.shape[1])
+        self.rt.ops.stream_centred_norm(residual, y, w, b, eps, mult, rows, self.weight, self.bias, self.spec.eps, out)
+        return out
+
+    def add_norm(self, residual: torch.Tensor, delta) -> torch.Tensor:
+        return self._run(residual, delta, None)
+
+    def gather_add_norm(self, residual: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        return self._run(residual, delta, rows)
+
+
 class StreamCopy:
     """What a block that norms after the sum hands to the next block in place of a pending delta:
     nothing is left to add, and ``values`` is the residual stream rounded to the compute dtype

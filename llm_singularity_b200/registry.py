@@ -111,6 +111,8 @@ def _register_builtin() -> None:
     register_architecture(FogezenConfig.architecture, FogezenConfig)
     from .config.fikizen import FikizenConfig
     register_architecture(FikizenConfig.architecture, FikizenConfig)
+    from .config.zinizen import ZinizenConfig
+    register_architecture(ZinizenConfig.architecture, ZinizenConfig)
 
 
 _register_builtin()
