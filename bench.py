@@ -359,7 +359,7 @@ def main():
     ap.add_argument("--windows", type=int, default=5, help="timed windows of K steps; the median is reported")
     ap.add_argument("--no-more", action="store_true", help="leave out the 3B and 8B serving runs")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--design", default=None, choices=["ridotar", "fogezen", "fikizen"],
+    ap.add_argument("--design", default=None, choices=["ridotar", "fogezen", "fikizen", "zinizen"],
                     help="instead of the headline: prefill and decode throughput of this design beside the "
                          "Llama decoder at equal size (llm_singularity_b200/measure/designs.py)")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: sizes to run, comma-separated")

@@ -215,6 +215,8 @@ struct AttnParams {
     int sink;                     // one more place with score 0 and no value in every softmax
     const bf16* gate;             // [tokens, heads] with this row stride: out *= sigmoid(gate), one number a head (or null)
     long long gate_stride;
+    float softcap;                // > 0: a scaled score s becomes softcap * tanh(s / softcap)
+    int linear_bias;              // head h's score for a key d positions back loses 2^(-8 (h + 1) / nh) * d
 };
 
 template <int HD>
@@ -433,7 +435,14 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int pos = p0 + il;
         const bool live = il < rows;
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
-        const float sc = prm.scale * kLog2e;
+        // Scores that are capped or lowered with the distance are finished here in natural units (the scale
+        // taken first), and only the change of base is left for the exponent.  tanh z = 1 - 2 / (1 + e^(2 z))
+        // on the special-function unit (ex2 and an approximate reciprocal: about 1e-7 absolute, times the cap
+        // far below what the bfloat16 operands of Q K^T leave).
+        const bool modified = prm.softcap > 0.f || prm.linear_bias != 0;
+        const float slope = prm.linear_bias ? exp2f(-8.f * (float)(h + 1) / (float)prm.nh) : 0.f;
+        const float cap2 = prm.softcap > 0.f ? 2.f / prm.softcap : 0.f;
+        const float sc = modified ? kLog2e : prm.scale * kLog2e;
         // m is the reference maximum of the exponents (log2 domain), l the sum of 2^(s - m).  O
         // accumulates in TMEM over all tiles; it is rescaled only when a row's maximum has grown
         // by more than kRescale since its reference was set, so most tiles never touch O here.
@@ -474,6 +483,15 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tmem_ld_wait();
             warp_arrive(&s_free[t & 1], lane);                 // S of the tile after the next may overwrite this one
             // columns of this tile the row may see: [c_lo, c_hi]
+            if (modified) {
+                const float dist0 = (float)(pos - key0);            // distance to the tile's first key
+#pragma unroll
+                for (int x = 0; x < kKeys; ++x) {
+                    float sv = __uint_as_float(v[x]) * prm.scale;
+                    if (prm.softcap > 0.f) sv = prm.softcap * (1.f - __fdividef(2.f, 1.f + __expf(sv * cap2)));
+                    v[x] = __float_as_uint(sv - slope * (dist0 - (float)x));
+                }
+            }
             const int c_hi = full ? kKeys - 1 : (live ? pos - key0 : -1);
             const int c_lo = (full || prm.window <= 0) ? 0 : pos - prm.window + 1 - key0;
             float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -654,12 +672,15 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 // Every request of the step is processed (single decode tokens too, as 1-row tiles, unless
 // skip_single).
-LSB_API int lsb_prefill_attention_tc5(const void* qkv, int qkv_stride, int n_tokens, const void* k_pages,
-                                      const void* v_pages, const int* q_start, const int* kv_len,
-                                      const int* table_rows, const int* block_table, int table_stride, void* out,
-                                      int n_requests, int max_q_len, int nh, int nkv, int hd, int page_size,
-                                      int num_pages, float scale, int window, int skip_single, int sink,
-                                      const void* gate, long long gate_stride, cudaStream_t stream) {
+// `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap); `linear_bias`: head h's score for a key d
+// positions back then loses 2^(-8 (h + 1) / nh) * d.
+LSB_API int lsb_prefill_attention_tc5_biased(const void* qkv, int qkv_stride, int n_tokens, const void* k_pages,
+                                             const void* v_pages, const int* q_start, const int* kv_len,
+                                             const int* table_rows, const int* block_table, int table_stride, void* out,
+                                             int n_requests, int max_q_len, int nh, int nkv, int hd, int page_size,
+                                             int num_pages, float scale, int window, int skip_single, int sink,
+                                             const void* gate, long long gate_stride, float softcap, int linear_bias,
+                                             cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (!lsb_prefill_attention_tc5_supported(qkv, qkv_stride, k_pages, v_pages, nh, nkv, hd, page_size) ||
         n_requests > 65535 || (max_q_len + kRows - 1) / kRows > 65535)
@@ -685,9 +706,21 @@ LSB_API int lsb_prefill_attention_tc5(const void* qkv, int qkv_stride, int n_tok
     prm.table_stride = table_stride; prm.out = (bf16*)out; prm.nh = nh; prm.nkv = nkv;
     prm.page_size = page_size; prm.num_pages = num_pages; prm.scale = scale; prm.window = window; prm.skip_single = skip_single;
     prm.sink = sink; prm.gate = (const bf16*)gate; prm.gate_stride = gate_stride;
+    prm.softcap = softcap; prm.linear_bias = linear_bias;
     int sh = 0;
     while ((1 << sh) < page_size) ++sh;
     prm.page_shift = sh;
     dim3 grid(nh, (max_q_len + kRows - 1) / kRows, n_requests);
     return hd == 64 ? launch<64>(mq, mk, mv, prm, grid, stream) : launch<128>(mq, mk, mv, prm, grid, stream);
+}
+
+LSB_API int lsb_prefill_attention_tc5(const void* qkv, int qkv_stride, int n_tokens, const void* k_pages,
+                                      const void* v_pages, const int* q_start, const int* kv_len,
+                                      const int* table_rows, const int* block_table, int table_stride, void* out,
+                                      int n_requests, int max_q_len, int nh, int nkv, int hd, int page_size,
+                                      int num_pages, float scale, int window, int skip_single, int sink,
+                                      const void* gate, long long gate_stride, cudaStream_t stream) {
+    return lsb_prefill_attention_tc5_biased(qkv, qkv_stride, n_tokens, k_pages, v_pages, q_start, kv_len, table_rows,
+                                            block_table, table_stride, out, n_requests, max_q_len, nh, nkv, hd, page_size,
+                                            num_pages, scale, window, skip_single, sink, gate, gate_stride, 0.f, 0, stream);
 }

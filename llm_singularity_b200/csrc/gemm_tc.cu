@@ -150,7 +150,8 @@ struct GemmParams {
     int splits;                   // > 1: the blocks of one tile form a cluster along z
     int out_f32;                  // output element type
     int swiglu;                   // 0: plain; 1: weight rows alternate gate/up along j; 2: along i.
-    int act;                      // gated products: 1 silu, 2 gelu (tanh form), 3 none (gate * up)
+    int act;                      // gated products: 1 silu, 2 gelu (tanh form), 3 none (gate * up), 5 capped
+    float limit;                  // ... whose cap this is
                                   // The output then has half as many columns: silu(gate) * up.
     int static_operand;           // 1: P holds weights, 2: Q does (loaded before the PDL wait)
     void* out;                    // bf16 or float
@@ -181,13 +182,18 @@ __device__ __forceinline__ void load_acc(uint32_t tmem_base, int q, int c0, bool
 // expression with another exponent, g / (1 + e^(-2 c (g + 0.044715 g^3))), c = sqrt(2 / pi).  The
 // division must be the approximate one: for very negative gates 1 + e^-g is huge or infinite and
 // an IEEE reciprocal drops into its slow denormal path, which cost 15 us per tile on random data.
-enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3 };
-__device__ __forceinline__ float gate_mul(float g, float u, int act) {
+// The capped form with a limit L: g' = min(g, L), u' = clamp(u, -L, L), g' / (1 + e^(-1.702 g')) * (u' + 1).
+enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3, LSB_ACT_CAPPED_GLU = 5 };
+__device__ __forceinline__ float gate_mul(float g, float u, int act, float limit) {
     if (act == LSB_ACT_NONE) return g * u;
+    if (act == LSB_ACT_CAPPED_GLU) {
+        g = fminf(g, limit);
+        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (fminf(fmaxf(u, -limit), limit) + 1.f);
+    }
     const float a = act == LSB_ACT_GELU_TANH ? 1.5957691216f * (g + 0.044715f * g * g * g) : g;
     return __fdividef(g, 1.f + __expf(-a)) * u;
 }
-#define silu_mul(g, u) gate_mul((g), (u), prm.act)
+#define silu_mul(g, u) gate_mul((g), (u), prm.act, prm.limit)
 
 template <typename T> __device__ __forceinline__ void put(void* base, long long off, float v);
 template <> __device__ __forceinline__ void put<float>(void* base, long long off, float v) {
@@ -936,12 +942,15 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn
 
 // out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, bf16 or float output.
 // swiglu != 0: w has 2 * N_out rows alternating gate_i, up_i; out is [M, N / 2] with
-// out[m, i] = act(d[m, 2i]) * d[m, 2i + 1], act named by swiglu: 1 silu, 2 gelu (tanh form), 3 none.
+// out[m, i] = act(d[m, 2i]) * d[m, 2i + 1], act named by swiglu: 1 silu, 2 gelu (tanh form), 3 none, 5 capped
+// (with its limit).
+static bool known_act(int act) { return (act >= 0 && act <= LSB_ACT_NONE) || act == LSB_ACT_CAPPED_GLU; }
+
 LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
-                        int swiglu, cudaStream_t stream) {
+                        int swiglu, float limit, cudaStream_t stream) {
     if (!lsb_gemm_tc_supported(x, w, M, N, K)) return (int)cudaErrorInvalidValue;
     if (swiglu && (N % 2)) return (int)cudaErrorInvalidValue;
-    if (swiglu < 0 || swiglu > LSB_ACT_NONE) return (int)cudaErrorInvalidValue;
+    if (!known_act(swiglu)) return (int)cudaErrorInvalidValue;
     int swap, bn, splits;
     lsb_gemm_tc_plan(M, N, K, swiglu, &swap, &bn, &splits);
     const int n_out = swiglu ? N / 2 : N;
@@ -953,6 +962,7 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     prm.out_f32 = out_f32;
     prm.out = out;
     prm.act = swiglu;
+    prm.limit = limit;
     prm.tile_group = nullptr;
     prm.group_rows = 0;
     const int sms = num_sms();
@@ -1040,10 +1050,10 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
 // (tile_group[M / 128], device memory, -1 for an unused tile), w stacks `groups` matrices [N, K];
 // out[m] = x[m] w[group of m's tile]^T, gated as above if swiglu.  M is a multiple of 128.
 LSB_API int lsb_gemm_tc_grouped(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
-                                int groups, const int* tile_group, int swiglu, cudaStream_t stream) {
+                                int groups, const int* tile_group, int swiglu, float limit, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (!lsb_gemm_tc_supported(x, w, M, N, K) || M % kBM || groups <= 0 || !tile_group) return (int)cudaErrorInvalidValue;
-    if ((swiglu && (N % 2)) || swiglu < 0 || swiglu > LSB_ACT_NONE) return (int)cudaErrorInvalidValue;
+    if ((swiglu && (N % 2)) || !known_act(swiglu)) return (int)cudaErrorInvalidValue;
     if ((long long)groups * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
     const int n_out = swiglu ? N / 2 : N;
     GemmParams prm;
@@ -1054,6 +1064,7 @@ LSB_API int lsb_gemm_tc_grouped(const void* x, const void* w, void* out, int out
     prm.out_f32 = out_f32;
     prm.out = out;
     prm.act = swiglu;
+    prm.limit = limit;
     prm.tile_group = tile_group;
     prm.group_rows = N;
     prm.rows_p = M; prm.rows_q = N; prm.ldc_i = n_out; prm.ldc_j = 1;

@@ -14,6 +14,8 @@
 // one row per request slot each; both are zero when a request begins, so the zeros before a sequence's
 // start and the first token's S_(t-1) = 0 need no special case.
 //
+// Long portions are walked in segments side by side (see rglru_segment_kernel).
+//
 // Three kernels: the convolution (a thread per token and channel); the gates (the same, in place:
 // the two gate products become a_t and the input sqrt(1 - a_t^2) i_t u_t, the y branch becomes its
 // activation); the walk (a thread per request and channel, tokens in order, three loads and one
@@ -130,6 +132,129 @@ rglru_walk_kernel(const float* __restrict__ gates, const float* __restrict__ pro
         // (increasing j reads entries j + n > j of the old state: none has been written yet)
         cs[(size_t)j * width] = back <= n ? proj[(size_t)(end - back) * ld + x_off + c] + xb : cs[(size_t)(j + n) * width];
     }
+}
+
+// Long portions in segments walked side by side.  A token's step is S <- a S + in, so a segment walked from
+// zero gives E (its own contribution) and the product P of its a's; the chain start(s + 1) = P_s start(s) + E_s
+// runs over the segments of a request in order (and leaves the new state and the convolution's last inputs
+// in the slot, as the single walk does); then every segment is walked again from its start for the outputs.
+// seg_pe: [requests * segs, 2, width] (P, then E; the chain writes a segment's start over its P).
+__global__ void __launch_bounds__(64)
+rglru_segment_kernel(const float* __restrict__ gates, const int* __restrict__ q_start, int seg_len, int segs,
+                     float* __restrict__ seg_pe, int width, int bw) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y / segs, sg = blockIdx.y % segs;
+    if (c >= width) return;
+    const int first = q_start[r] + sg * seg_len, end = min(q_start[r + 1], first + seg_len);
+    if (first >= end) return;
+    const int b = c / bw, o = c - b * bw;
+    const float* g = gates + (size_t)b * 2 * bw + o;
+    float P = 1.f, E = 0.f;
+    for (int t0 = first; t0 < end; t0 += kWalkAhead) {
+        float a[kWalkAhead], in[kWalkAhead];
+#pragma unroll
+        for (int j = 0; j < kWalkAhead; ++j) {
+            const bool live = t0 + j < end;
+            a[j] = live ? g[(size_t)(t0 + j) * 2 * width] : 1.f;
+            in[j] = live ? g[(size_t)(t0 + j) * 2 * width + bw] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < kWalkAhead; ++j) {
+            E = a[j] * E + in[j];
+            P *= a[j];
+        }
+    }
+    float* pe = seg_pe + ((size_t)blockIdx.y * 2) * width + c;
+    pe[0] = P;
+    pe[width] = E;
+}
+
+__global__ void __launch_bounds__(64)
+rglru_chain_kernel(float* __restrict__ seg_pe, const float* __restrict__ proj, long long ld, int x_off,
+                   const float* __restrict__ x_bias, int taps, float* __restrict__ state, float* __restrict__ conv_state,
+                   const int* __restrict__ q_start, const int* __restrict__ table_rows, int slots, int seg_len, int segs,
+                   int width) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= width) return;
+    const int first = q_start[r], end = q_start[r + 1];
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= slots) {
+        lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    float S = state[(size_t)slot * width + c];
+    const int n = end - first, used = (n + seg_len - 1) / seg_len;
+    for (int sg = 0; sg < used; ++sg) {
+        float* pe = seg_pe + ((size_t)(r * segs + sg) * 2) * width + c;
+        const float P = pe[0], E = pe[width];
+        pe[0] = S;
+        S = P * S + E;
+    }
+    state[(size_t)slot * width + c] = S;
+    const int keep = taps - 1;
+    const float xb = x_bias ? x_bias[c] : 0.f;
+    float* cs = conv_state + (size_t)slot * keep * width + c;
+    for (int j = 0; j < keep; ++j) {
+        const int back = keep - j;
+        cs[(size_t)j * width] = back <= n ? proj[(size_t)(end - back) * ld + x_off + c] + xb : cs[(size_t)(j + n) * width];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(64)
+rglru_segment_out_kernel(const float* __restrict__ gates, const float* __restrict__ proj, long long ld, int y_off,
+                         const float* __restrict__ seg_pe, const int* __restrict__ q_start, int seg_len, int segs,
+                         T* __restrict__ out, int width, int bw) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y / segs, sg = blockIdx.y % segs;
+    if (c >= width) return;
+    const int first = q_start[r] + sg * seg_len, end = min(q_start[r + 1], first + seg_len);
+    if (first >= end) return;
+    const int b = c / bw, o = c - b * bw;
+    const float* g = gates + (size_t)b * 2 * bw + o;
+    float S = seg_pe[((size_t)blockIdx.y * 2) * width + c];
+    for (int t0 = first; t0 < end; t0 += kWalkAhead) {
+        float a[kWalkAhead], in[kWalkAhead], y[kWalkAhead];
+#pragma unroll
+        for (int j = 0; j < kWalkAhead; ++j) {
+            const int t = t0 + j;
+            const bool live = t < end;
+            a[j] = live ? g[(size_t)t * 2 * width] : 1.f;
+            in[j] = live ? g[(size_t)t * 2 * width + bw] : 0.f;
+            y[j] = live ? proj[(size_t)t * ld + y_off + c] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < kWalkAhead; ++j) {
+            S = a[j] * S + in[j];
+            if (t0 + j < end) out[(size_t)(t0 + j) * width + c] = lsb_from_float<T>(S * y[j]);
+        }
+    }
+}
+
+// seg_pe: 32-bit scratch of n_requests * ceil(max_q_len / seg_len) * 2 * width numbers
+LSB_API int lsb_rglru_walk_segments(const float* gates, const float* proj, long long ld, int x_off, int y_off,
+                                    const float* x_bias, int taps, float* state, float* conv_state, const int* q_start,
+                                    const int* table_rows, int slots, void* out, int dtype, int width, int blocks,
+                                    int n_requests, int max_q_len, int seg_len, float* seg_pe, cudaStream_t stream) {
+    if (n_requests <= 0 || max_q_len <= 0) return 0;
+    if (width <= 0 || blocks <= 0 || width % blocks || taps <= 0 || seg_len <= 0 || !seg_pe) return (int)cudaErrorInvalidValue;
+    const int segs = (max_q_len + seg_len - 1) / seg_len;
+    if ((long long)n_requests * segs > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid((width + 63) / 64, n_requests * segs);
+    int rc = lsb_launch(rglru_segment_kernel, grid, dim3(64), 0, stream, 1, gates, q_start, seg_len, segs, seg_pe, width,
+                        width / blocks);
+    if (rc) return rc;
+    rc = lsb_launch(rglru_chain_kernel, dim3((width + 63) / 64, n_requests), dim3(64), 0, stream, 1, seg_pe, proj, ld, x_off,
+                    x_bias, taps, state, conv_state, q_start, table_rows, slots, seg_len, segs, width);
+    if (rc) return rc;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(rglru_segment_out_kernel<T>, grid, dim3(64), 0, stream, 1, gates, proj, ld,
+                                                y_off, (const float*)seg_pe, q_start, seg_len, segs, (T*)out, width,
+                                                width / blocks));
+    return 0;
 }
 
 LSB_API int lsb_rglru_conv(const float* proj, long long ld, int x_off, const float* x_bias, const float* w,

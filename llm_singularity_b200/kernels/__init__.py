@@ -299,8 +299,9 @@ def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], ro
 
 
 ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3, "capped_glu": 5}     # act(gate) * up of a gated product
-# "capped_glu" has a limit L: min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1).  The products'
-# epilogues do not know it: such a product leaves gate and up side by side and the activation kernel follows.
+# "capped_glu" has a limit L: min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1).  The tile kernel's
+# epilogue knows it (prompt steps, the experts' grouped product); where another kernel makes the product it
+# leaves gate and up side by side and the activation kernel follows.
 UNFUSED_GATED = ("capped_glu",)
 
 
@@ -415,6 +416,20 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     if gated and activation in UNFUSED_GATED:
         if into is not None:
             raise KernelError("linear: a product into the residual is plain and in the compute dtype")
+        if not limit > 0:
+            raise KernelError(f"linear: '{activation}' needs a positive limit")
+        if isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] > 16 \
+                and w.shape[0] % 2 == 0 and tensor_core_gemm_ok(x, w) and (out_dtype or x.dtype) in (x.dtype, torch.float32):
+            # the tile kernel's epilogue knows the capped form; steps of a few rows take the plain way below
+            _req(w, "w", x.dtype, 2)
+            if w.shape[1] != x.shape[1]:
+                raise KernelError(f"linear: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+            _chain_ends()
+            od = out_dtype or x.dtype
+            out = torch.empty((x.shape[0], w.shape[0] // 2), dtype=od, device=x.device)
+            _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if od == torch.float32 else 0),
+                  _i(x.shape[0]), _i(w.shape[0]), _i(x.shape[1]), _i(_activation_id(activation)), _f(limit), _stream(out))
+            return out
         raw = linear(x, w, out_dtype)
         half = torch.empty((raw.shape[0], raw.shape[1] // 2), dtype=raw.dtype, device=raw.device)
         gated_activation(raw, half, activation, limit)
@@ -484,7 +499,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
-              _i(M), _i(N), _i(K), _i(act), _stream(out))
+              _i(M), _i(N), _i(K), _i(act), _f(0.0), _stream(out))
         return out
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _call("gemm", "lsb_gemm_nt", _p(x), _p(w), _p(out), _i(_dt(x)), _i(_dt(out)), _i(M), _i(N), _i(K),
@@ -1109,6 +1124,10 @@ def rglru_gates(gates: torch.Tensor, r_bias: Optional[torch.Tensor], i_bias: Opt
           _ll(proj.stride(0)), _i(y_off), _p(y_bias), _i(width), _i(blocks), _i(T), _stream(u))
 
 
+RGLRU_SEGMENT = 64              # tokens of a segment when long portions of the recurrence are walked in segments (0: never)
+RGLRU_SEGMENT_FROM = 256        # ... in steps whose longest portion has at least this many tokens
+
+
 def rglru_walk(gates: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, x_bias: Optional[torch.Tensor],
                taps: int, state: torch.Tensor, conv_state: torch.Tensor, ctx, out: torch.Tensor, blocks: int) -> None:
     """S <- a_t S + in_t token by token for every request and channel, from the slot's ``state`` [slots, width] and
@@ -1124,6 +1143,20 @@ def rglru_walk(gates: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, 
             or conv_state.shape[0] != state.shape[0] or conv_state.shape[2] != width \
             or (taps > 1 and conv_state.shape[1] != taps - 1) or max(x_off, y_off) + width > proj.shape[1]:
         raise KernelError("rglru_walk: gates, proj, the states and out disagree")
+    if RGLRU_SEGMENT and ctx.max_q_len >= RGLRU_SEGMENT_FROM \
+            and ctx.n_requests * -(-ctx.max_q_len // RGLRU_SEGMENT) <= 65535:
+        # a step with a long portion: every request's tokens in segments walked side by side, chained, and
+        # walked again from their starts (the single tokens of other requests are segments of one token)
+        segs = -(-ctx.max_q_len // RGLRU_SEGMENT)
+        key = ("rglru", out.device, ctx.n_requests * segs * 2 * width)
+        scratch = _scratch.get(key)
+        if scratch is None:
+            scratch = _scratch[key] = torch.empty(key[2], dtype=torch.float32, device=out.device)
+        _call("rglru", "lsb_rglru_walk_segments", _p(gates), _p(proj), _ll(proj.stride(0)), _i(x_off), _i(y_off),
+              _p(x_bias), _i(taps), _p(state), _p(conv_state), _p(ctx.q_start), _p(ctx.table_rows), _i(state.shape[0]),
+              _p(out), _i(_dt(out)), _i(width), _i(blocks), _i(ctx.n_requests), _i(ctx.max_q_len), _i(RGLRU_SEGMENT),
+              _p(scratch), _stream(out))
+        return
     _call("rglru", "lsb_rglru_walk", _p(gates), _p(proj), _ll(proj.stride(0)), _i(x_off), _i(y_off), _p(x_bias),
           _i(taps), _p(state), _p(conv_state), _p(ctx.q_start), _p(ctx.table_rows), _i(state.shape[0]), _p(out),
           _i(_dt(out)), _i(width), _i(blocks), _i(ctx.n_requests), _stream(out))
@@ -1357,19 +1390,20 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
     # where they all come before the portions (as the scheduler puts them), go on below
     n_req, max_q = ctx.n_requests, ctx.max_q_len
     if (USE_TCGEN05_ATTENTION and DV_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
-            and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128 and not softcap and not linear_bias
+            and not chunk and (gate is None or gate_per_head) and ctx.max_q_len >= 128
             and cache.page_size in (8, 16, 32, 64)
             and _lib("attention_tc5").lsb_prefill_attention_tc5_supported(
                 _p(q), _i(q.shape[1]), _p(cache.k_pages), _p(cache.v_pages), _i(nh), _i(nkv), _i(dk), _i(cache.page_size))):
         n_decode, first, last = _batch_shape(ctx)
         if n_decode == 0 or (n_decode == first and last == ctx.n_requests):
             off = 4 * first
-            _call("attention_tc5", "lsb_prefill_attention_tc5", _p(q), _i(q.shape[1]), _i(T), _p(cache.k_pages),
+            _call("attention_tc5", "lsb_prefill_attention_tc5_biased", _p(q), _i(q.shape[1]), _i(T), _p(cache.k_pages),
                   _p(cache.v_pages), ctypes.c_void_p(ctx.q_start.data_ptr() + off),
                   ctypes.c_void_p(ctx.kv_len.data_ptr() + off), ctypes.c_void_p(ctx.table_rows.data_ptr() + off),
                   _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests - first),
                   _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale),
-                  _i(window), _i(0), _i(1 if sink else 0), _p(gate), _ll(gate_stride), _stream(out))
+                  _i(window), _i(0), _i(1 if sink else 0), _p(gate), _ll(gate_stride), _f(softcap),
+                  _i(1 if linear_bias else 0), _stream(out))
             if first == 0:
                 return
             n_req, max_q = first, 1
@@ -1754,18 +1788,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         _call("moe", "lsb_moe_gather", _p(x), _i(_dt(x)), _p(pos), _p(weights), _i(on_input), _i(T), _i(top),
               _i(cap_tiles * tile), _i(H), _p(rows), s)
         _chain_ends()
-        if unfused:
-            # (gate and up leave the product side by side; rows of unused tiles hold whatever the buffer held,
-            # and nothing reads what becomes of them)
-            raw = torch.empty(cap_tiles * tile, 2 * F, dtype=x.dtype, device=dev)
-            _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(raw), _i(0), _i(cap_tiles * tile),
-                  _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(0), s)
-            gated_activation(raw, hidden, activation, limit)
-        else:
-            _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),
-                  _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(_activation_id(activation)), s)
+        _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),
+              _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(_activation_id(activation)), _f(limit), s)
         _call("gemm_tc", "lsb_gemm_tc_grouped", _p(hidden), _p(w_down), _p(y), _i(0), _i(cap_tiles * tile),
-              _i(H), _i(F), _i(E), _p(tile_expert), _i(0), s)
+              _i(H), _i(F), _i(E), _p(tile_expert), _i(0), _f(0.0), s)
     else:
         _call("moe", "lsb_moe_up", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input), _p(w_gate_up),
               _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), _f(limit), s)

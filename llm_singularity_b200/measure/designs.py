@@ -1,4 +1,10 @@
-"""Prefill and decode throughput of a design (Ridotar, Fogezen, Fikizen) beside the Llama decoder at equal size.
+"""Prefill and decode throughput of a design (Ridotar, Fogezen, Fikizen, Zinizen) beside the Llama decoder at equal size.
+
+Zinizen: layers cycling through the RG-LRU block, biased capped attention that shares values between
+its layers, gated latent attention and the biased attention once more; the first layer's feed-forward
+is dense, the others route every token to ``top`` of ``experts`` capped gated experts beside a shared
+one.  It is also run beside Ridotar, the design closest to it (routed experts, latent attention, a
+recurrence walked token by token).
 
 Fikizen: layers cycling through windowed sink attention with a gate per head, the gated
 delta-rule memory behind short convolutions (no feed-forward), the parallel pair (normed windowed
@@ -96,9 +102,32 @@ def fikizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
             "layers": out}
 
 
-DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config, "fikizen": fikizen_config}
+def zinizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
+    heads = width // 128
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "scale": 1.5},
+           "shared": {"ff": ff, "limit": 5.0}}
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "softcap": 50.0, "q_temp": {"coef": 0.1, "every": 512}, "v_mix": True}
+    latent = {"heads": heads, "dim": 128, "vdim": 128, "rot_dim": 64, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
+              "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192)}
+    recurrent = {"width": width, "blocks": heads, "conv": 4}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        mlp = {"kind": "dense", "ff": top * ff} if i == 0 else moe
+        if kind == 0:
+            out.append({"type": "rglru", "mixer": dict(recurrent), "mlp": mlp})
+        elif kind == 2:
+            out.append({"type": "latent_attention", "mixer": dict(latent), "mlp": mlp})
+        else:
+            out.append({"type": "attention", "mixer": dict(attention), "mlp": mlp})
+    return {"architecture": "Zinizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+
+
+DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config, "fikizen": fikizen_config, "zinizen": zinizen_config}
 # the designs each is also measured beside (Llama always is)
-CLOSEST = {"fikizen": ("fogezen",)}
+CLOSEST = {"fikizen": ("fogezen",), "zinizen": ("ridotar",)}
 
 
 def llama_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
