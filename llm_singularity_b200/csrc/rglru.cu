@@ -7,7 +7,9 @@
 //     log a_t = -c * r_t * softplus(lam)        a_t = exp(log a_t)
 //     S_t = a_t S_(t-1) + sqrt(1 - a_t^2) * i_t * u_t        out_t = S_t * act(y_t + b_y)
 //
-// All of it is 32-bit: the projections arrive in 32-bit, the convolution sums, the gates, decays, the
+// All of it is 32-bit (with one split: where the gates' maps are bfloat16, u enters their products on the
+// tensor cores as the sum of two bfloat16 numbers, 16 bits of mantissa, see rglru_conv_kernel; the 32-bit
+// path multiplies u as it is): the projections arrive in 32-bit, the convolution sums, the gates, decays, the
 // state and the product with the other branch are formed in 32-bit, and only out is rounded to the
 // compute dtype.  sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits where a is
 // close to one.  A request's state is S (one number a channel) and the x branch's last taps - 1 inputs,
@@ -32,7 +34,7 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, long long ld, 
                                   const float* __restrict__ conv_bias, int taps, const float* __restrict__ conv_state,
                                   const int* __restrict__ token_req, const int* __restrict__ q_start,
                                   const int* __restrict__ table_rows, int slots, float* __restrict__ u, int width,
-                                  int tokens) {
+                                  int tokens, __nv_bfloat16* __restrict__ split, int bw) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
@@ -55,6 +57,16 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, long long ld, 
         acc += w[(size_t)c * taps + k] * x;
     }
     u[(size_t)t * width + c] = acc;
+    if (split) {
+        // u as the sum of two bfloat16 numbers (the rounded value and the rounded rest: 16 bits of mantissa
+        // together), side by side per block, [t, b, hi(bw) | lo(bw)]: the operand of a tensor-core product
+        // against the gates' maps repeated along k, whose 32-bit sums then hold u's digits
+        const int b = c / bw, o = c - b * bw;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(acc);
+        __nv_bfloat16* dst = split + (size_t)t * 2 * width + (size_t)b * 2 * bw + o;
+        dst[0] = hi;
+        dst[bw] = __float2bfloat16_rn(acc - __bfloat162float(hi));
+    }
 }
 
 __device__ __forceinline__ float rglru_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
@@ -260,12 +272,13 @@ LSB_API int lsb_rglru_walk_segments(const float* gates, const float* proj, long 
 LSB_API int lsb_rglru_conv(const float* proj, long long ld, int x_off, const float* x_bias, const float* w,
                            const float* conv_bias, int taps, const float* conv_state, const int* token_req,
                            const int* q_start, const int* table_rows, int slots, float* u, int width, int tokens,
-                           cudaStream_t stream) {
+                           void* split, int blocks, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (width <= 0 || taps <= 0 || tokens > 65535 * 32) return (int)cudaErrorInvalidValue;
-    if (tokens > 65535) return (int)cudaErrorInvalidValue;
+    if (tokens > 65535 || (split && (blocks <= 0 || width % blocks))) return (int)cudaErrorInvalidValue;
     return lsb_launch(rglru_conv_kernel, dim3((width + 127) / 128, tokens), dim3(128), 0, stream, 1, proj, ld, x_off,
-                      x_bias, w, conv_bias, taps, conv_state, token_req, q_start, table_rows, slots, u, width, tokens);
+                      x_bias, w, conv_bias, taps, conv_state, token_req, q_start, table_rows, slots, u, width, tokens,
+                      (__nv_bfloat16*)split, split ? width / blocks : width);
 }
 
 LSB_API int lsb_rglru_gates(float* gates, const float* r_bias, const float* i_bias, const float* lam, float rate,

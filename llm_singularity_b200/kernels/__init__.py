@@ -1076,11 +1076,18 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
 
 # ------------------------------------------------------- gated linear recurrent unit (real gates)
 def rglru_conv(proj: torch.Tensor, x_off: int, x_bias: Optional[torch.Tensor], taps_w: torch.Tensor,
-               conv_bias: Optional[torch.Tensor], conv_state: torch.Tensor, ctx, u: torch.Tensor) -> None:
+               conv_bias: Optional[torch.Tensor], conv_state: torch.Tensor, ctx, u: torch.Tensor,
+               split: Optional[torch.Tensor] = None, blocks: int = 1) -> None:
     """u[t, c] = conv_bias[c] + sum_k taps_w[c, k] * xin[t - (taps - 1 - k), c] with xin = proj[:, x_off + c] +
     x_bias[c]; before a portion's first token xin is the request slot's ``conv_state`` [slots, taps - 1, width]
-    (zeros before a sequence's start).  All 32-bit."""
+    (zeros before a sequence's start).  All 32-bit.  ``split`` (bfloat16 [T, 2 * width]): u once more as the sum
+    of two bfloat16 numbers, per block of ``width / blocks`` channels the rounded values and then the rounded
+    rests."""
     _req(proj, "proj", torch.float32, 2)
+    if split is not None:
+        _req(split, "split", torch.bfloat16, 2)
+        if split.shape != (u.shape[0], 2 * u.shape[1]) or blocks <= 0 or u.shape[1] % blocks:
+            raise KernelError("rglru_conv: split must be [tokens, 2 * width], the blocks dividing the width")
     _req(taps_w, "taps_w", torch.float32, 2)
     _req(conv_state, "conv_state", torch.float32, 3)
     _req(u, "u", torch.float32, 2)
@@ -1098,7 +1105,7 @@ def rglru_conv(proj: torch.Tensor, x_off: int, x_bias: Optional[torch.Tensor], t
                 raise KernelError(f"rglru_conv: {name} must have {width} entries")
     _call("rglru", "lsb_rglru_conv", _p(proj), _ll(proj.stride(0)), _i(x_off), _p(x_bias), _p(taps_w), _p(conv_bias),
           _i(taps), _p(conv_state), _p(ctx.token_req), _p(ctx.q_start), _p(ctx.table_rows), _i(conv_state.shape[0]),
-          _p(u), _i(width), _i(T), _stream(u))
+          _p(u), _i(width), _i(T), _p(split), _i(blocks), _stream(u))
 
 
 def rglru_gates(gates: torch.Tensor, r_bias: Optional[torch.Tensor], i_bias: Optional[torch.Tensor],

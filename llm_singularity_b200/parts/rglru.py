@@ -9,9 +9,12 @@ parts; in each, two square matrices give the recurrence's gates, ``r = sigmoid(R
 
 and ``W_o (S * y)`` is the block's result.  S starts at zero when a request takes a slot, and so do
 the convolution's last ``conv_taps - 1`` inputs, which are state too; both live in ``StateSpec`` rows,
-32-bit.  The product of the two branches leaves in 32-bit, and the convolution, the gates' products
-(multiply-adds on unrounded u), sigmoid, softplus, the exponential, the square root, the state and
-the product with y are all formed in 32-bit; only what enters W_o is rounded to the compute dtype.
+32-bit.  The product of the two branches leaves in 32-bit, and the convolution, the gates' products,
+sigmoid, softplus, the exponential, the square root, the state and the product with y are all formed
+in 32-bit; only what enters W_o is rounded to the compute dtype.  The gates' products: in 32-bit
+storage multiply-adds on u as it is; with bfloat16 maps u enters the tensor cores as the sum of two
+bfloat16 numbers (the rounded value and the rounded rest, 16 bits of mantissa) against the maps
+repeated along k, so that the 32-bit sums carry u's digits and nothing is rounded to bfloat16's 8.
 """
 from __future__ import annotations
 
@@ -34,6 +37,8 @@ class RGLRU(Part):
             raise ValueError(f"{s.blocks} blocks do not divide a width of {s.width}")
         if s.conv_taps < 1:
             raise ValueError(f"conv_taps must be at least 1, got {s.conv_taps}")
+        if rt.dtype == torch.bfloat16:
+            self.kernels = self.kernels + ("latent_tc",)
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
@@ -50,6 +55,9 @@ class RGLRU(Part):
         self.w_in = torch.cat([tensors["y"], tensors["x"]], dim=0).contiguous()          # rows: y, then x
         # per block the rows of R_b, then those of I_b: one product makes both gates' inputs
         self.w_gates = torch.cat([tensors["ra"], tensors["ri"]], dim=1).contiguous()     # [B, 2 bw, bw]
+        self.split = self.w_gates.dtype == torch.bfloat16
+        if self.split:                                  # the same maps for the rounded u and for its rest
+            self.w_gates = torch.cat([self.w_gates, self.w_gates], dim=2).contiguous()   # [B, 2 bw, 2 bw]
         self.w_out = tensors["o"].contiguous()
         self.taps = tensors["conv"].contiguous()
         self.vecs = {n: tensors[n].reshape(-1).contiguous() for n in ("y_bias", "x_bias", "conv_bias", "ra_bias",
@@ -66,9 +74,14 @@ class RGLRU(Part):
         proj = ops.linear(x, self.w_in, out_dtype=f32)                     # [T, y | x]
         state, conv_state = cache[0].state, cache[1].state
         u = self.rt.empty(T, N, dtype=f32)
-        ops.rglru_conv(proj, N, v["x_bias"], self.taps, v["conv_bias"], conv_state, ctx, u)
         gates = self.rt.empty(T, 2 * N, dtype=f32)
-        ops.batched_nt(u.view(T, B, N // B), self.w_gates, gates.view(T, B, 2 * (N // B)), exact=True)
+        if self.split:
+            halves = self.rt.empty(T, 2 * N, dtype=torch.bfloat16)
+            ops.rglru_conv(proj, N, v["x_bias"], self.taps, v["conv_bias"], conv_state, ctx, u, split=halves, blocks=B)
+            ops.batched_nt(halves.view(T, B, 2 * (N // B)), self.w_gates, gates.view(T, B, 2 * (N // B)))
+        else:
+            ops.rglru_conv(proj, N, v["x_bias"], self.taps, v["conv_bias"], conv_state, ctx, u)
+            ops.batched_nt(u.view(T, B, N // B), self.w_gates, gates.view(T, B, 2 * (N // B)), exact=True)
         ops.rglru_gates(gates, v["ra_bias"], v["ri_bias"], v["lam"], s.rate, u, proj, 0, v["y_bias"], B)
         out = self.rt.empty(T, N)
         ops.rglru_walk(gates, proj, N, 0, v["x_bias"], s.conv_taps, state, conv_state, ctx, out, B)

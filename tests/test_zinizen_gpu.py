@@ -435,9 +435,19 @@ def test_recurrence_kernels_carry_state_and_inputs(dtype, width, blocks, taps, m
         pj = torch.cat([proj[s][lo:hi] for s, lo, hi in cuts]).cuda().contiguous()
         T = pj.shape[0]
         u = torch.empty(T, width, device="cuda")
-        K.rglru_conv(pj, width, f("x.b"), W["conv"].float().cuda().contiguous(), f("conv.b"), conv_state, ctx, u)
         gates = torch.empty(T, 2 * width, device="cuda")
-        K.batched_nt(u.view(T, blocks, bw), w_gates, gates.view(T, blocks, 2 * bw), exact=True)
+        if dtype == torch.bfloat16:          # u as two bfloat16 numbers against the maps repeated along k
+            halves = torch.empty(T, 2 * width, dtype=dtype, device="cuda")
+            K.rglru_conv(pj, width, f("x.b"), W["conv"].float().cuda().contiguous(), f("conv.b"), conv_state, ctx, u,
+                         split=halves, blocks=blocks)
+            K.batched_nt(halves.view(T, blocks, 2 * bw), torch.cat([w_gates, w_gates], dim=2).contiguous(),
+                         gates.view(T, blocks, 2 * bw))
+            exact = torch.empty_like(gates)
+            K.batched_nt(u.view(T, blocks, bw), w_gates, exact.view(T, blocks, 2 * bw), exact=True)
+            assert (gates - exact).abs().max() < 2e-4 * max(1.0, exact.abs().max().item())
+        else:
+            K.rglru_conv(pj, width, f("x.b"), W["conv"].float().cuda().contiguous(), f("conv.b"), conv_state, ctx, u)
+            K.batched_nt(u.view(T, blocks, bw), w_gates, gates.view(T, blocks, 2 * bw), exact=True)
         K.rglru_gates(gates, f("ra.b"), f("ri.b"), f("lam"), 8.0, u, pj, 0, f("y.b"), blocks)
         out = torch.empty(T, width, dtype=dtype, device="cuda")
         K.rglru_walk(gates, pj, width, 0, f("x.b"), taps, state, conv_state, ctx, out, blocks)
