@@ -484,12 +484,19 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             warp_arrive(&s_free[t & 1], lane);                 // S of the tile after the next may overwrite this one
             // columns of this tile the row may see: [c_lo, c_hi]
             if (modified) {
-                const float dist0 = (float)(pos - key0);            // distance to the tile's first key
+                // cap tanh(z) = cap - 2 cap / (1 + e^(2 z)); the distance to key x of the tile is dist0 - x
+                const float off = -slope * (float)(pos - key0);
+                if (prm.softcap > 0.f) {
+                    const float c1 = prm.scale * cap2 * kLog2e, m2cap = -2.f * prm.softcap, base = prm.softcap + off;
 #pragma unroll
-                for (int x = 0; x < kKeys; ++x) {
-                    float sv = __uint_as_float(v[x]) * prm.scale;
-                    if (prm.softcap > 0.f) sv = prm.softcap * (1.f - __fdividef(2.f, 1.f + __expf(sv * cap2)));
-                    v[x] = __float_as_uint(sv - slope * (dist0 - (float)x));
+                    for (int x = 0; x < kKeys; ++x) {
+                        const float r = __fdividef(1.f, 1.f + fast_exp2(__uint_as_float(v[x]) * c1));
+                        v[x] = __float_as_uint(fmaf(slope, (float)x, fmaf(m2cap, r, base)));
+                    }
+                } else {
+#pragma unroll
+                    for (int x = 0; x < kKeys; ++x)
+                        v[x] = __float_as_uint(fmaf(slope, (float)x, fmaf(__uint_as_float(v[x]), prm.scale, off)));
                 }
             }
             const int c_hi = full ? kKeys - 1 : (live ? pos - key0 : -1);

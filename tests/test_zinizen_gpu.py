@@ -290,19 +290,21 @@ def _fill(cache, row, K, V):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh, nkv, dk, dv, cap, page", [(4, 2, 32, 16, 7.0, 16), (6, 2, 96, 48, 0.0, 16), (3, 3, 10, 14, 2.5, 8),
                                                         (4, 1, 64, 64, 11.0, 16), (2, 2, 128, 128, 30.0, 32), (8, 2, 64, 64, 0.0, 16)])
-def test_capped_biased_attention_kernel_one_score_standing_out(dtype, nh, nkv, dk, dv, cap, page):
+@pytest.mark.parametrize("single_first", [False, True])
+def test_capped_biased_attention_kernel_one_score_standing_out(dtype, nh, nkv, dk, dv, cap, page, single_first):
     """Three requests in one launch (a prompt portion, a single token, a long whole prompt).  All keys
     are alike but one per request, which every query scores high, up to the cap: the heads with a small
     slope then take its value from far back, the heads with a large slope prefer near keys.  The
     standing-out key is put far back, on a page border, first in the sequence and last."""
     from llm_singularity_b200 import kernels as K
     g = torch.Generator().manual_seed(dk + dv)
-    q_lens, kv_lens = [37, 1, 170], [90, 131, 170]
-    ctx = _ctx(q_lens, kv_lens, rows=[2, 0, 1])
+    q_lens, kv_lens = ([1, 37, 170], [131, 90, 170]) if single_first else ([37, 1, 170], [90, 131, 170])
+    slot_rows = [0, 2, 1] if single_first else [2, 0, 1]
+    ctx = _ctx(q_lens, kv_lens, rows=slot_rows)
     scale = 1.0 / math.sqrt(dk)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], dtype=F64)
-    for targets in ([3, 0, 15], [16, 127, 48], [0, 64, 0], [89, 130, 169]):
+    for targets in ([3, 0, 15], [16, 64, 48], [0, 79, 0], [89, 89, 169]):
         cache = _pages(3, 176, nkv, dk, dv, page, dtype, seed=1)
         qs, outs = [], []
         for r, (ql, kv, tgt) in enumerate(zip(q_lens, kv_lens, targets)):
@@ -312,7 +314,7 @@ def test_capped_biased_attention_kernel_one_score_standing_out(dtype, nh, nkv, d
             q = 0.1 * torch.randn(ql, nh, dk, generator=g)
             q[:, :, 0] = 1.5 / scale
             Kd, Vd, q = (t.to(dtype).double() for t in (Kd, Vd, q))
-            _fill(cache, [2, 0, 1][r], Kd, Vd)
+            _fill(cache, slot_rows[r], Kd, Vd)
             pos_q, pos_k = torch.arange(kv - ql, kv), torch.arange(kv)
             seen = pos_k[None, :] <= pos_q[:, None]
             o = torch.zeros(ql, nh, dv, dtype=F64)
