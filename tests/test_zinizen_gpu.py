@@ -503,3 +503,50 @@ def test_capped_gated_product(dtype, T):
     tol = 1e-5 if dtype == torch.float32 else 3e-2
     assert (got.double().cpu() - want).abs().max() < tol
     K.check_status()
+
+
+# ------------------------------------------------------------------------ as a user runs it
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_as_a_user_runs_it(tmp_path, dtype):
+    """bin/trace_run as a process of its own, fed step by step: seven requests through four slots
+    and a pool smaller than their sum (mixed portions and single tokens), then each request in
+    portions of changing size; every position against the plain model."""
+    import cuttings
+    import numpy as np
+    import replay_util
+    cfg = U.CONFIGS["mix_a"]
+    W, path = _setup(tmp_path, cfg, 23)
+    seqs = {f"q{i}": U.tokens_for(cfg, n, 60 + i) for i, n in enumerate((5, 70, 33, 1, 100, 64, 21))}
+    want = {rid: U.plain_logits(cfg, W, t) for rid, t in seqs.items()}
+    for k, (steps, max_tokens) in enumerate((cuttings.mixed(seqs, seed=3), cuttings.portions(seqs))):
+        out = str(tmp_path / f"out{k}")
+        replay_util.replay_subprocess(path, dtype, steps, out, max_tokens)
+        rows = replay_util.collect(steps, out, cfg["vocab"])
+        assert len(rows) == sum(len(t) for t in seqs.values())
+        for rid, t in seqs.items():
+            got = torch.from_numpy(np.stack([rows[(rid, p)] for p in range(len(t))]))
+            assert U.close(got, want[rid], dtype), (k, rid, U.rel_err(got, want[rid]))
+
+
+def test_command_line_serves_the_design(tmp_path):
+    """bin/llm-serve-llama picks the design by config.json and generates greedily what the plain
+    model picks (where its choice is clear)."""
+    cfg = U.CONFIGS["mix_b"]
+    W, path = _setup(tmp_path, cfg, 29)
+    prompts = [U.tokens_for(cfg, n, 70 + n) for n in (4, 19)]
+    (tmp_path / "p.json").write_text(json.dumps(prompts))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", path, "--dtype", "fp32",
+           "--prompt-ids", str(tmp_path / "p.json"), "--max-new-tokens", "6", "--ignore-eos",
+           "--num-kv-blocks", "16", "--max-batch-size", "2"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    outs = [json.loads(line)["tokens"] for line in res.stdout.splitlines()]
+    assert len(outs) == 2 and all(len(o) == 6 for o in outs)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:
+            logits = U.plain_logits(cfg, W, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if top2[0] - top2[1] > 0.05:
+                assert tok == int(logits.argmax())
+            seq.append(tok)
