@@ -53,7 +53,7 @@ constexpr int kWarmBytes = 112 * 1024;          // of the next product's weights
 constexpr int kTailBytes = 320;                // barriers, the give-up flag, the rows' scales
 static_assert(3 * kMaxStages * 8 + 16 + 16 * 4 <= kTailBytes, "barriers, flag and scales fit the tail");
 constexpr int kFoldBytes = (16 * 128 + kWarps * 128 + 16) * 4;   // more shared memory if the product adds to the residual
-enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3 };
+enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3, LSB_ACT_CAPPED_GLU = 5 };
 
 struct StreamParams {
     const bf16* x;
@@ -62,6 +62,7 @@ struct StreamParams {
     int M, N, K;
     int out_f32;
     int act;            // 0: plain product; else the activation of a gated product
+    float limit;        // the cap of LSB_ACT_CAPPED_GLU: min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
     int kc;             // K per stage (a multiple of 128)
     int stages;
     int unit;           // rows are dealt in units of this many (2 for a gated product)
@@ -146,6 +147,13 @@ __device__ __forceinline__ float gate_act(float g, int act) {
     if (act == LSB_ACT_SILU) return g / (1.f + __expf(-g));
     if (act == LSB_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
     return g;
+}
+__device__ __forceinline__ float gate_times_up(float g, float u, int act, float limit) {
+    if (act == LSB_ACT_CAPPED_GLU) {
+        g = fminf(g, limit);
+        return g / (1.f + __expf(-1.702f * g)) * (fminf(fmaxf(u, -limit), limit) + 1.f);
+    }
+    return gate_act(g, act) * u;
 }
 
 // A pass covers 16 * rt rows of the block (rt = 1, 2, 4 or 8 tiles); the eight consumer warps are
@@ -288,11 +296,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // for the first weights.
     int e_M = prm.M, e_N = prm.N, e_act = prm.act, e_f32 = prm.out_f32;
     void* e_out = prm.out;
-    float e_inv = prm.inv_size, e_eps = prm.eps;
+    float e_inv = prm.inv_size, e_eps = prm.eps, e_limit = prm.limit;
     float* e_res = prm.residual;
     const float* e_nw = prm.norm_w;
     float* e_ss = prm.ss_out;
-    asm volatile("" : "+r"(e_M), "+r"(e_N), "+r"(e_act), "+r"(e_f32), "+l"(e_out), "+f"(e_inv), "+f"(e_eps),
+    asm volatile("" : "+r"(e_M), "+r"(e_N), "+r"(e_act), "+r"(e_f32), "+l"(e_out), "+f"(e_inv), "+f"(e_eps), "+f"(e_limit),
                       "+l"(e_res), "+l"(e_nw), "+l"(e_ss));
     const int n_out = e_act ? e_N / 2 : e_N;
     const int k_steps = kc >> 4;               // a multiple of kInFlight (beyond K the copy has filled in zeros)
@@ -395,7 +403,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     g += src[(size_t)p * part_stride];
                     u += src[(size_t)p * part_stride + width];
                 }
-                v = gate_act(g * scale, e_act) * (u * scale);
+                v = gate_times_up(g * scale, u * scale, e_act, e_limit);
             } else {
                 const float* src = buf + (size_t)j * width + m;
                 v = 0.f;
@@ -449,7 +457,7 @@ static int sm_count() {
 // least two stages within the shared-memory budget.
 static int make_plan(int M, int N, int K, int act, int fold, int sms, Plan* p) {
     if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 64) return 0;
-    if (act < 0 || act > LSB_ACT_NONE || (act && (N % 2))) return 0;
+    if (act < 0 || (act > LSB_ACT_NONE && act != LSB_ACT_CAPPED_GLU) || (act && (N % 2))) return 0;
     p->unit = act ? 2 : 1;
     const int units = N / p->unit;
     p->blocks = units < sms ? units : sms;
@@ -563,11 +571,12 @@ static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& 
 //
 // warm != null: a StreamWarm that lsb_gemm_stream_warm filled in for the streaming product that
 // follows this one in the stream; its first weights are pulled toward L2 while this one ends.
-LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
-                                   int act, const float* ss_in, int ss_parts, int size, float eps,
-                                   float* residual, const float* norm_w, float* ss_out, const void* warm,
-                                   cudaStream_t stream) {
+static int stream_product(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                          int act, float limit, const float* ss_in, int ss_parts, int size, float eps,
+                          float* residual, const float* norm_w, float* ss_out, const void* warm,
+                          cudaStream_t stream) {
     Plan p;
+    if (act == LSB_ACT_CAPPED_GLU && !(limit > 0.f)) return (int)cudaErrorInvalidValue;
     if (!lsb_gemm_stream_supported(x, w, M, N, K, act)) return (int)cudaErrorInvalidValue;
     if (ss_in && (ss_parts <= 0 || ss_parts > 32 * kSsPerLane || size <= 0)) return (int)cudaErrorInvalidValue;
     if (residual && (act || out_f32 || !norm_w || !ss_out)) return (int)cudaErrorInvalidValue;
@@ -575,7 +584,7 @@ LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int 
     StreamParams prm;
     prm.x = (const bf16*)x; prm.w = (const bf16*)w; prm.out = out;
     prm.M = M; prm.N = N; prm.K = K;
-    prm.out_f32 = out_f32; prm.act = act;
+    prm.out_f32 = out_f32; prm.act = act; prm.limit = limit;
     prm.kc = p.kc; prm.stages = p.stages; prm.unit = p.unit; prm.w_bytes = p.w_bytes;
     prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c;
     prm.rt = p.rt;
@@ -596,6 +605,21 @@ LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int 
     if (ss_in || residual)
         return p.nt == 1 ? launch<1, true>(maps, prm, p, wm, stream) : launch<2, true>(maps, prm, p, wm, stream);
     return p.nt == 1 ? launch<1, false>(maps, prm, p, wm, stream) : launch<2, false>(maps, prm, p, wm, stream);
+}
+
+LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                                   int act, const float* ss_in, int ss_parts, int size, float eps,
+                                   float* residual, const float* norm_w, float* ss_out, const void* warm,
+                                   cudaStream_t stream) {
+    return stream_product(x, w, out, out_f32, M, N, K, act, 0.f, ss_in, ss_parts, size, eps, residual, norm_w, ss_out,
+                          warm, stream);
+}
+
+// The gated product whose activation has a limit (act LSB_ACT_CAPPED_GLU), nothing folded in.
+LSB_API int lsb_gemm_stream_capped(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                                   float limit, const void* warm, cudaStream_t stream) {
+    return stream_product(x, w, out, out_f32, M, N, K, LSB_ACT_CAPPED_GLU, limit, nullptr, 0, 0, 0.f, nullptr, nullptr,
+                          nullptr, warm, stream);
 }
 
 // Fills `out` (sizeof(StreamWarm) bytes, see lsb_stream_warm_bytes) with what the kernel before a

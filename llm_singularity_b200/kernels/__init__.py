@@ -300,8 +300,9 @@ def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], ro
 
 ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3, "capped_glu": 5}     # act(gate) * up of a gated product
 # "capped_glu" has a limit L: min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1).  The tile kernel's
-# epilogue knows it (prompt steps, the experts' grouped product); where another kernel makes the product it
-# leaves gate and up side by side and the activation kernel follows.
+# epilogue knows it (prompt steps, the experts' grouped product) and so does the streaming product's (steps of
+# a few rows); where another kernel makes the product (32-bit, sizes those two refuse) it leaves gate and up
+# side by side and the activation kernel follows.
 UNFUSED_GATED = ("capped_glu",)
 
 
@@ -429,6 +430,16 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
             out = torch.empty((x.shape[0], w.shape[0] // 2), dtype=od, device=x.device)
             _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if od == torch.float32 else 0),
                   _i(x.shape[0]), _i(w.shape[0]), _i(x.shape[1]), _i(_activation_id(activation)), _f(limit), _stream(out))
+            return out
+        act5 = _activation_id(activation)
+        if isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 16 \
+                and STREAM_PRODUCTS and w.dim() == 2 and w.dtype == x.dtype and w.shape[1] == x.shape[1] \
+                and (out_dtype or x.dtype) in (x.dtype, torch.float32) and stream_gemm_ok(x, w, act5):
+            # a few rows: the streaming product's end knows the capped form too
+            od = out_dtype or x.dtype
+            out = torch.empty((x.shape[0], w.shape[0] // 2), dtype=od, device=x.device)
+            _call("gemm_stream", "lsb_gemm_stream_capped", _p(x), _p(w), _p(out), _i(1 if od == torch.float32 else 0),
+                  _i(x.shape[0]), _i(w.shape[0]), _i(x.shape[1]), _f(limit), _warm_after(w, True, x.shape[0]), _stream(out))
             return out
         raw = linear(x, w, out_dtype)
         half = torch.empty((raw.shape[0], raw.shape[1] // 2), dtype=raw.dtype, device=raw.device)
