@@ -242,7 +242,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos,
                                    const float* __restrict__ wts, int on_output, int top, int n,
-                                   int capacity, T* __restrict__ out) {
+                                   int capacity, T* __restrict__ out, const T* __restrict__ add) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const size_t t = blockIdx.x;
@@ -254,6 +254,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
             const float v = lsb_to_float(y[(size_t)p * n + i]);
             s += on_output ? wts[t * top + k] * v : v;
         }
+        if (add) s += lsb_to_float(add[t * n + i]);          // (what every token passes besides its chosen experts)
         out[t * n + i] = lsb_from_float<T>(s);
     }
 }
@@ -321,15 +322,15 @@ LSB_API int lsb_moe_down(const void* h, int dtype, const int* row_token, const v
 
 // y_same: the expert rows are stored in the output's type (the tensor-core path), else 32-bit
 LSB_API int lsb_moe_combine(const void* y, int y_same, const int* pos, const float* wts, int on_output,
-                            int n_tokens, int top, int n, int capacity, void* out, int dtype,
+                            int n_tokens, int top, int n, int capacity, void* out, int dtype, const void* add,
                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     LSB_DISPATCH_DTYPE(dtype, {
         if (y_same)
             return lsb_launch(moe_combine_kernel<T, T>, dim3(n_tokens), dim3(256), 0, stream, 1, (const T*)y, pos,
-                              wts, on_output, top, n, capacity, (T*)out);
+                              wts, on_output, top, n, capacity, (T*)out, (const T*)add);
         return lsb_launch(moe_combine_kernel<T, float>, dim3(n_tokens), dim3(256), 0, stream, 1, (const float*)y,
-                          pos, wts, on_output, top, n, capacity, (T*)out);
+                          pos, wts, on_output, top, n, capacity, (T*)out, (const T*)add);
     });
     return 0;
 }

@@ -1741,7 +1741,7 @@ MOE_FUSED_ROUTING_TOKENS = 256  # steps of at most this many tokens choose their
 def moe_routed_experts(x: torch.Tensor, logits: torch.Tensor, top: int, score: str, renormalize: bool,
                        w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str, weight_on: str,
                        out: torch.Tensor, choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
-                       renorm_eps: float = 0.0, limit: float = 0.0) -> None:
+                       renorm_eps: float = 0.0, limit: float = 0.0, add: Optional[torch.Tensor] = None) -> None:
     """``moe_route`` on the 32-bit ``logits`` followed by ``moe_experts``; in a step of few tokens the
     choosing rides in the kernel that sorts the rows by expert (one launch less)."""
     _req(logits, "logits", torch.float32, 2)
@@ -1753,17 +1753,18 @@ def moe_routed_experts(x: torch.Tensor, logits: torch.Tensor, top: int, score: s
     if T <= MOE_FUSED_ROUTING_TOKENS:
         moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out,
                     route=(logits, MOE_SCORES[score], 1 if renormalize else 0, choice_bias, weight_scale, renorm_eps),
-                    limit=limit)
+                    limit=limit, add=add)
     else:
         moe_route(logits, top, score, renormalize, ids, weights, choice_bias, weight_scale, renorm_eps)
-        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out, limit=limit)
+        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out, limit=limit, add=add)
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor, route=None,
-                limit: float = 0.0) -> None:
+                limit: float = 0.0, add: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum over k of down_e(act(gate_e u) * up_e u), e = ids[t, k], with u = weights[t, k] * x[t]
-    (``weight_on`` "input") or u = x[t] and the sum weighted ("output").  ``w_gate_up`` [E, 2F, H] has
+    (``weight_on`` "input") or u = x[t] and the sum weighted ("output"); plus ``add[t]`` if given (a shared
+    expert's rows), in the same 32-bit sum.  ``w_gate_up`` [E, 2F, H] has
     rows alternating gate_i, up_i; ``w_down`` [E, H, F]."""
     _req(x, "x", dim=2)
     _req(ids, "ids", torch.int32, 2)
@@ -1772,6 +1773,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     _req(w_down, "w_down", x.dtype, 3)
     _req(out, "out", x.dtype, 2)
     T, H = x.shape
+    if add is not None:
+        _req(add, "add", x.dtype, 2)
+        if add.shape != (T, H):
+            raise KernelError("moe_experts: add must have out's shape")
     E, F2, _ = w_gate_up.shape
     F, top = F2 // 2, ids.shape[1]
     if w_gate_up.shape != (E, 2 * F, H) or w_down.shape != (E, H, F) or out.shape != (T, H) \
@@ -1816,7 +1821,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
               _p(y), _i(H), _i(F), s)
     _call("moe", "lsb_moe_combine", _p(y), _i(1 if tc else 0), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top),
-          _i(H), _i(cap_tiles * tile), _p(out), _i(_dt(out)), s)
+          _i(H), _i(cap_tiles * tile), _p(out), _i(_dt(out)), _p(add), s)
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,

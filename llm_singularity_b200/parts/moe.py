@@ -7,7 +7,8 @@ says so, divided by their sum.  A score multiplies what the spec names: the expe
 (``u = s x``; with a gated expert that is not the same as scaling its output) or its output.
 With ``choice_bias`` a learnt number per expert joins the scores for the choice only; the chosen
 scores are divided by their sum + ``renorm_eps`` and multiplied by ``weight_scale``.  ``shared``: a
-gated feed-forward that every token passes besides its chosen experts; the two results are added.
+gated feed-forward that every token passes besides its chosen experts; its rows join the 32-bit sum
+over the chosen experts' rows in the combining kernel.
 
 The experts' matrices are stacked (``[E, 2F, H]`` with rows alternating gate_i, up_i, and
 ``[E, H, F]``); a step's (token, choice) pairs are sorted by expert on the device into row
@@ -42,7 +43,7 @@ class RoutedExperts(Part):
         shared = getattr(s, "shared", None)
         self.shared = FEED_FORWARDS.build(shared, rt) if shared is not None else None
         if self.shared is not None:
-            self.kernels = self.kernels + ("activation", "sandwich")
+            self.kernels = self.kernels + ("activation",)
 
     def children(self) -> Dict[str, Part]:
         return {"shared": self.shared} if self.shared is not None else {}
@@ -80,10 +81,8 @@ class RoutedExperts(Part):
         for name, default in (("weight_scale", 1.0), ("renorm_eps", 0.0), ("limit", 0.0)):
             if getattr(s, name, default) != default:
                 extra[name] = float(getattr(s, name))
+        if self.shared is not None:                 # its rows join the sum over the chosen experts
+            extra["add"] = self.shared.forward(x, ctx)
         ops.moe_routed_experts(x, logits, s.top, s.score, s.renormalize, self.w_gate_up, self.w_down,
                                s.activation, s.weight_on, out, **extra)
-        if self.shared is None:
-            return out
-        both = self.rt.empty(T, s.hidden_size)
-        ops.branch_sum([out, self.shared.forward(x, ctx)], [1.0, 1.0], both)
-        return both
+        return out
