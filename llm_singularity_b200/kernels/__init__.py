@@ -1764,7 +1764,8 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
                 limit: float = 0.0, add: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum over k of down_e(act(gate_e u) * up_e u), e = ids[t, k], with u = weights[t, k] * x[t]
     (``weight_on`` "input") or u = x[t] and the sum weighted ("output"); plus ``add[t]`` if given (a shared
-    expert's rows), in the same 32-bit sum.  ``w_gate_up`` [E, 2F, H] has
+    expert's rows, or a callable that makes them: it is called behind the experts' products), in the same
+    32-bit sum.  ``w_gate_up`` [E, 2F, H] has
     rows alternating gate_i, up_i; ``w_down`` [E, H, F]."""
     _req(x, "x", dim=2)
     _req(ids, "ids", torch.int32, 2)
@@ -1773,10 +1774,6 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     _req(w_down, "w_down", x.dtype, 3)
     _req(out, "out", x.dtype, 2)
     T, H = x.shape
-    if add is not None:
-        _req(add, "add", x.dtype, 2)
-        if add.shape != (T, H):
-            raise KernelError("moe_experts: add must have out's shape")
     E, F2, _ = w_gate_up.shape
     F, top = F2 // 2, ids.shape[1]
     if w_gate_up.shape != (E, 2 * F, H) or w_down.shape != (E, H, F) or out.shape != (T, H) \
@@ -1820,6 +1817,12 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
               _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), _f(limit), s)
         _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
               _p(y), _i(H), _i(F), s)
+    if callable(add):           # made now, behind the experts' products (its own products' weights are then the
+        add = add()             # last streamed before the next layer's, which they ask L2 for while they end)
+    if add is not None:
+        _req(add, "add", x.dtype, 2)
+        if add.shape != (T, H):
+            raise KernelError("moe_experts: add must have out's shape")
     _call("moe", "lsb_moe_combine", _p(y), _i(1 if tc else 0), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top),
           _i(H), _i(cap_tiles * tile), _p(out), _i(_dt(out)), _p(add), s)
 

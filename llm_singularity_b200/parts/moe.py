@@ -82,7 +82,7 @@ class RoutedExperts(Part):
             if getattr(s, name, default) != default:
                 extra[name] = float(getattr(s, name))
         if self.shared is not None:                 # its rows join the sum over the chosen experts
-            extra["add"] = self.shared.forward(x, ctx)
+            extra["add"] = lambda: self.shared.forward(x, ctx)
         ops.moe_routed_experts(x, logits, s.top, s.score, s.renormalize, self.w_gate_up, self.w_down,
                                s.activation, s.weight_on, out, **extra)
         return out
