@@ -104,10 +104,10 @@ def fikizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
 
 def zinizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
     heads = width // 128
-    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "scale": 1.5},
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "scale": 2.0},
            "shared": {"ff": ff, "limit": 5.0}}
     attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                 "softcap": 50.0, "q_temp": {"coef": 0.1, "every": 512}, "v_mix": True}
+                 "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 512}, "v_mix": True}
     latent = {"heads": heads, "dim": 128, "vdim": 128, "rot_dim": 64, "q_rank": 3 * width // 4, "kv_rank": kv_rank,
               "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192)}
     recurrent = {"width": width, "blocks": heads, "conv": 4}
@@ -122,7 +122,7 @@ def zinizen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
         else:
             out.append({"type": "attention", "mixer": dict(attention), "mlp": mlp})
     return {"architecture": "Zinizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 5}}, "layers": out}
 
 
 DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config, "fikizen": fikizen_config, "zinizen": zinizen_config}

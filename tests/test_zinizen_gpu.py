@@ -180,7 +180,7 @@ def test_far_keys_page_borders_and_first_tokens(tmp_path, dtype):
     """A strongly peaked softmax against pages of 16: a key that is lost, one page or one place off, or
     a first token left out changes the logits by far more than the tolerance.  The attention's heads
     differ in how fast they forget (the distance's slope), so some look far back and some do not."""
-    for kind, kw, seed in (("attention", dict(cap=60.0, temp=(0.3, 64)), 31), ("latent_attention", {}, 32),
+    for kind, kw, seed in (("attention", dict(cap=60.0, temp=(0.25, 48)), 31), ("latent_attention", {}, 32),
                            ("attention", dict(heads=8, kv=8, dim=16, vdim=16, cap=None), 33)):
         cfg = U.single(kind, mlp=None, **kw)
         W, path = _setup(tmp_path, cfg, seed, sharpen=8.0)
